@@ -147,6 +147,50 @@ class DecodeBatch(C.Structure):
                 ("logits_f32", C.c_void_p), ("next_tokens", C.c_void_p), ("next_logits", C.c_void_p)]
 
 
+
+class SigmoidAttnArgs(C.Structure):
+    """struct atoma_sigmoid_attn_args (include/atoma_hybrid.h)"""
+
+    _fields_ = ([(n, C.c_void_p) for n in ("q", "k_cache", "v_cache", "out", "positions", "token_seq", "block_tables",
+                                           "slopes", "head_bias", "talk")] +
+                [(n, C.c_int64) for n in ("T", "B", "max_blocks", "H", "G", "dim", "vdim", "block_size")] +
+                [("scale", C.c_float), ("softcap", C.c_float), ("dtype", C.c_uint32), ("max_query_len", C.c_int32)])
+
+
+class HybridLayer(C.Structure):
+    """struct atoma_hybrid_layer"""
+
+    _fields_ = ([("mixer", C.c_int32), ("has_mlp", C.c_int32)] +
+                [(n, C.c_void_p) for n in ("norm1", "norm1b", "norm2", "norm2b")] +
+                [(n, C.c_int64) for n in ("heads", "kv_heads", "dim", "vdim", "temp_every")] +
+                [("scale", C.c_float), ("softcap", C.c_float), ("temp_coef", C.c_float)] +
+                [(n, C.c_void_p) for n in ("w_qkv", "b_qkv", "q_norm", "k_norm", "talk", "head_bias", "slopes",
+                                           "k_cache", "v_cache")] +
+                [("state_width", C.c_int64)] +
+                [(n, C.c_void_p) for n in ("w_zxg", "b_zxg", "state", "w_o")] +
+                [("ff", C.c_int64), ("act", C.c_int32), ("w_gate_up", C.c_void_p), ("w_down", C.c_void_p)])
+
+
+class HybridModel(C.Structure):
+    """struct atoma_hybrid_model"""
+
+    _fields_ = ([(n, C.c_int64) for n in ("width", "vocab", "num_layers", "block_size")] +
+                [("eps", C.c_float), ("logit_scale", C.c_float), ("norm_offset", C.c_float), ("dtype", C.c_uint32)] +
+                [(n, C.c_void_p) for n in ("embed", "inv_freq", "final_norm", "head")] +
+                [("layers", C.POINTER(HybridLayer))])
+
+
+class HybridBatch(C.Structure):
+    """struct atoma_hybrid_batch"""
+
+    _fields_ = ([(n, C.c_int64) for n in ("num_tokens", "num_seqs", "num_selected", "max_blocks")] +
+                [("max_query_len", C.c_int32)] +
+                [(n, C.c_void_p) for n in ("tokens", "positions", "slot_mapping", "token_seq", "query_start", "context_lens",
+                                           "block_tables", "state_slots", "selected", "scratch")] +
+                [("scratch_bytes", C.c_int64)] +
+                [(n, C.c_void_p) for n in ("logits", "next_tokens", "residual_trace")])
+
+
 # Exact C parameter lists, in header order.
 _RUN_MHA_ARGS = [
     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,  # q k v o lse alibi
@@ -237,6 +281,20 @@ SIGNATURES = {
                                                                         C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_void_p]),
     "atoma_gemm_tn_add_rmsnorm": (None, [C.c_void_p] * 3 + [C.c_int64] * 6 + [C.c_void_p] * 4 + [C.c_int64] * 3 +
                                   [C.c_float, C.c_uint32, C.c_void_p]),
+    # atoma_hybrid.h
+    "atoma_embed_sinusoid": (None, [C.c_void_p] * 5 + [C.c_int64] * 3 + [C.c_uint32, C.c_void_p]),
+    "atoma_rmsnorm_rows": (None, [C.c_void_p] * 3 + [C.c_float, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_postnorm_add_prenorm": (None, [C.c_void_p] * 5 + [C.c_int64, C.c_int64, C.c_float, C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_qk_norm_cache": (None, [C.c_void_p] * 9 + [C.c_int64] * 5 + [C.c_float, C.c_float, C.c_int64, C.c_uint32, C.c_void_p]),
+    "atoma_sigmoid_attention_paged": (None, [C.POINTER(SigmoidAttnArgs), C.c_void_p]),
+    "atoma_mingru_scan": (None, [C.c_void_p] * 7 + [C.c_int64] * 3 + [C.c_int32, C.c_uint32, C.c_void_p]),
+    "atoma_glu": (None, [C.c_void_p] * 2 + [C.c_int64] * 2 + [C.c_int32, C.c_uint32, C.c_void_p]),
+    "atoma_linear": (None, [C.c_void_p] * 3 + [C.c_int64] * 3 + [C.c_uint32, C.c_void_p]),
+    "atoma_scale_logits_greedy": (None, [C.c_void_p] * 3 + [C.c_int64] * 2 + [C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_hybrid_abi_sizeof": (C.c_int64, [C.c_int]),
+    "atoma_hybrid_scratch_bytes": (C.c_int64, [C.POINTER(HybridModel), C.c_int64, C.c_int64]),
+    "atoma_hybrid_step": (None, [C.POINTER(HybridModel), C.POINTER(HybridBatch), C.c_void_p]),
+    "atoma_debug_hybrid": (None, [C.c_int]),
     # atoma_ops.h
     "atoma_flash_attn_plan": (C.c_char_p, [C.POINTER(Tensor)] * 4 + [C.c_float, C.c_int64, C.c_int64, C.c_float,
                                                                     C.c_int, C.POINTER(MhaPlan)]),
@@ -287,6 +345,30 @@ def load(path: os.PathLike | str | None = None) -> C.CDLL:
         fn.restype = res
         fn.argtypes = args
     return lib
+
+
+def ensure_built(verbose: bool = True) -> None:
+    """Builds lib/libflashattention.so from csrc/ when it is missing or was built from other sources (a fresh
+    checkout holds no binaries).  Needs nvcc; everything is compiled for sm_100a."""
+    import shutil
+    import subprocess
+    import sys
+    if LIB_PATH.exists():
+        try:
+            have = C.CDLL(str(LIB_PATH), mode=C.RTLD_LOCAL)
+            have.atoma_source_hash.restype = C.c_char_p
+            if have.atoma_source_hash().decode() == source_hash():
+                return
+        except (OSError, AttributeError):
+            pass
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cmd = ["make", "-C", str(_PKG / "csrc"), "-j", str(min(16, os.cpu_count() or 4)), "shared", f"NVCC={nvcc}"]
+    if verbose:
+        print("building", LIB_PATH, file=sys.stderr, flush=True)
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout[-8000:])
+        raise ImportError(f"building {LIB_PATH} failed (exit code {r.returncode})")
 
 
 _LIB: C.CDLL | None = None

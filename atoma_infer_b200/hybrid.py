@@ -1,0 +1,268 @@
+"""Hybrid (attention + recurrent) decoder models: description, device layout and the step executor's host side.
+
+A model family (atoma_infer_b200/lilovik.py is the first) describes itself as a `HybridSpec` — a list of
+layers, each a mixer (sigmoid attention or minGRU) with its sizes and constants and an optional gated
+feed-forward — and hands over its weights under the generic names below.  `HybridExecutor` lays them out
+on the device, owns the paged key/value caches and the recurrent-state slots, and runs one step of a MIXED
+batch (portions of prompts beside single decoded tokens) through ONE C call, `atoma_hybrid_step`
+(csrc/hybrid_step.cu).  The step's integer inputs are built by the same `atoma_prepare_input` /
+`InputStager` that the Llama decode step uses (worker.py), with chunked prefill on.
+
+Weight layout (rows stacked so that one GEMM makes all projections of a sublayer):
+  w_qkv     [H dim + G dim + G vdim, width]   b_qkv   [same] float32
+  w_zxg     [3 S, width]                      b_zxg   [3 S] float32 (zero where the design has no bias)
+  w_gate_up [2 ff, width]                     w_down  [width, ff]
+  w_o       [width, H vdim] or [width, S]
+  norms, q/k norm weights, talking-heads matrix, per-head bias and distance slopes: float32.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence as Seq_
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import HybridBatch, HybridLayer, HybridModel
+from .ops import AtomaError
+from .scheduler import StepPlan
+from .worker import InputStager, SequenceInput
+
+MIXER_ATTENTION, MIXER_MINGRU = 0, 1
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+DTYPE_CODES = {torch.bfloat16: 1, torch.float32: 2}
+
+
+@dataclass(frozen=True)
+class AttentionSpec:
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    softcap: float = 0.0
+    temp_coef: float = 0.0
+    temp_every: int = 0            # 0 = no query temperature
+    slopes: Optional[Seq_[float]] = None   # per-head distance slopes; None = no distance bias
+
+
+@dataclass(frozen=True)
+class MinGruSpec:
+    width: int
+
+
+@dataclass(frozen=True)
+class MlpSpec:
+    ff: int
+    act: str = "relu"
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    mixer: str                               # "attention" | "mingru"
+    attention: Optional[AttentionSpec] = None
+    mingru: Optional[MinGruSpec] = None
+    mlp: Optional[MlpSpec] = None
+
+
+@dataclass(frozen=True)
+class HybridSpec:
+    width: int
+    vocab: int
+    eps: float
+    logit_scale: float
+    layers: Seq_[LayerSpec] = ()
+    norm_offset: float = 1.0                 # norm weights are stored as offsets from this value
+    position_base: float = 10000.0
+
+    @property
+    def has_state(self) -> bool:
+        return any(l.mixer == "mingru" for l in self.layers)
+
+    def cache_bytes_per_token(self, dtype: torch.dtype) -> int:
+        es = torch.empty((), dtype=dtype).element_size()
+        return sum(l.attention.kv_heads * (l.attention.dim + l.attention.vdim) * es for l in self.layers if l.mixer == "attention")
+
+
+@dataclass
+class StepOutput:
+    logits: Optional[torch.Tensor]           # float32 [num_selected, vocab] on the device (a view, valid until the next step)
+    next_tokens: Optional[torch.Tensor]      # int32 [num_selected]: greedy choice
+    rows: List[tuple] = field(default_factory=list)   # (seq_id, offset in its chunk) per selected row
+    residual_trace: Optional[torch.Tensor] = None
+
+
+class HybridExecutor:
+    """Device state of one hybrid model + `execute(plan)`."""
+
+    def __init__(self, spec: HybridSpec, weights: Dict[str, object], dtype: torch.dtype, device, num_blocks: int,
+                 block_size: int = 16, num_state_slots: int = 4):
+        if dtype not in DTYPE_CODES:
+            raise AtomaError(f"hybrid models run in bfloat16 or float32, not {dtype}")
+        if not torch.cuda.is_available():
+            raise AtomaError("hybrid models need a CUDA device: there is no CPU path")
+        self.spec, self.dtype, self.device = spec, dtype, torch.device(device)
+        self.block_size, self.num_blocks, self.num_state_slots = int(block_size), int(num_blocks), int(num_state_slots)
+        self._keep: List[torch.Tensor] = []
+        dev = self.device
+
+        def big(t):          # matrices: the activation format
+            t = t.to(dtype).contiguous().to(dev)
+            self._keep.append(t)
+            return t
+
+        def small(t):        # per-channel parameters: float32
+            t = torch.as_tensor(t).to(torch.float32).contiguous().to(dev)
+            self._keep.append(t)
+            return t
+
+        self.embed, self.head = big(weights["embed"]), big(weights["head"])
+        self.final_norm = small(weights["final_norm"])
+        half = (spec.width + 1) // 2
+        inv = np.array([spec.position_base ** (-2.0 * i / spec.width) for i in range(half)], dtype=np.float64)
+        self.inv_freq = torch.from_numpy(inv).to(dev)
+        self.k_caches: List[Optional[torch.Tensor]] = []
+        self.v_caches: List[Optional[torch.Tensor]] = []
+        self.states: List[Optional[torch.Tensor]] = []
+        self._layers = (HybridLayer * len(spec.layers))()
+        rows = self.num_blocks * self.block_size
+        for i, (ls, w) in enumerate(zip(spec.layers, weights["layers"])):
+            L = self._layers[i]
+            L.norm1, L.norm1b = small(w["norm1"]).data_ptr(), small(w["norm1b"]).data_ptr()
+            L.has_mlp = 1 if ls.mlp is not None else 0
+            kc = vc = st = None
+            if ls.mixer == "attention":
+                a = ls.attention
+                if a.heads % a.kv_heads:
+                    raise AtomaError(f"layer {i}: {a.kv_heads} kv heads do not divide {a.heads} heads")
+                L.mixer = MIXER_ATTENTION
+                L.heads, L.kv_heads, L.dim, L.vdim, L.temp_every = a.heads, a.kv_heads, a.dim, a.vdim, a.temp_every
+                L.scale, L.softcap, L.temp_coef = a.scale, a.softcap, a.temp_coef
+                L.w_qkv, L.b_qkv = big(w["w_qkv"]).data_ptr(), small(w["b_qkv"]).data_ptr()
+                L.q_norm, L.k_norm = small(w["q_norm"]).data_ptr(), small(w["k_norm"]).data_ptr()
+                L.talk = small(w["talk"]).data_ptr() if w.get("talk") is not None else None
+                L.head_bias = small(w["head_bias"] if w.get("head_bias") is not None else torch.zeros(a.heads)).data_ptr()
+                L.slopes = small(torch.tensor(list(a.slopes) if a.slopes is not None else [0.0] * a.heads)).data_ptr()
+                kc = torch.zeros((rows, a.kv_heads, a.dim), dtype=dtype, device=dev)
+                vc = torch.zeros((rows, a.kv_heads, a.vdim), dtype=dtype, device=dev)
+                L.k_cache, L.v_cache = kc.data_ptr(), vc.data_ptr()
+            elif ls.mixer == "mingru":
+                L.mixer = MIXER_MINGRU
+                L.state_width = ls.mingru.width
+                L.w_zxg, L.b_zxg = big(w["w_zxg"]).data_ptr(), small(w["b_zxg"]).data_ptr()
+                st = torch.zeros((max(1, self.num_state_slots), ls.mingru.width), dtype=torch.float32, device=dev)
+                L.state = st.data_ptr()
+            else:
+                raise AtomaError(f"layer {i}: unknown mixer {ls.mixer!r}")
+            L.w_o = big(w["w_o"]).data_ptr()
+            if ls.mlp is not None:
+                if ls.mlp.act not in ACTIVATIONS:
+                    raise AtomaError(f"layer {i}: unknown activation {ls.mlp.act!r}")
+                L.norm2, L.norm2b = small(w["norm2"]).data_ptr(), small(w["norm2b"]).data_ptr()
+                L.ff, L.act = ls.mlp.ff, ACTIVATIONS[ls.mlp.act]
+                L.w_gate_up, L.w_down = big(w["w_gate_up"]).data_ptr(), big(w["w_down"]).data_ptr()
+            self.k_caches.append(kc)
+            self.v_caches.append(vc)
+            self.states.append(st)
+        m = HybridModel()
+        m.width, m.vocab, m.num_layers, m.block_size = spec.width, spec.vocab, len(spec.layers), self.block_size
+        m.eps, m.logit_scale, m.norm_offset, m.dtype = spec.eps, spec.logit_scale, spec.norm_offset, DTYPE_CODES[dtype]
+        m.embed, m.inv_freq = self.embed.data_ptr(), self.inv_freq.data_ptr()
+        m.final_norm, m.head = self.final_norm.data_ptr(), self.head.data_ptr()
+        m.layers = C.cast(self._layers, C.POINTER(HybridLayer))
+        self._model = m
+        self._stager = InputStager(device=dev, block_size=self.block_size, enable_chunked_prefill=True)
+        self._extra_host = None
+        self._extra_dev = None
+        self._scratch = None
+        self._logits = None
+        self._next = None
+        self.launches_last_step = 0
+
+    # ---- buffers (grow-only) ----
+    def _reserve(self, T: int, S: int) -> None:
+        L = _lib.lib()
+        need = int(L.atoma_hybrid_scratch_bytes(C.byref(self._model), T, S))
+        if need < 0:
+            raise AtomaError("atoma_hybrid_scratch_bytes failed")
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=self.device)
+        if self._logits is None or self._logits.shape[0] < S:
+            cap = max(S, 8)
+            self._logits = torch.empty((cap, self.spec.vocab), dtype=torch.float32, device=self.device)
+            self._next = torch.zeros((cap,), dtype=torch.int32, device=self.device)
+
+    def _extras(self, token_seq: np.ndarray, state_slots: np.ndarray, selected: np.ndarray):
+        n = token_seq.size + state_slots.size + selected.size
+        if self._extra_host is None or self._extra_host.numel() < n:
+            cap = 1 << max(10, (n - 1).bit_length())
+            torch.cuda.synchronize(self.device)
+            self._extra_host = torch.empty(cap, dtype=torch.int32, pin_memory=True)
+            self._extra_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        else:
+            torch.cuda.current_stream(self.device).synchronize()   # the previous copy has read the pinned buffer
+        h = self._extra_host.numpy()
+        a, b = token_seq.size, token_seq.size + state_slots.size
+        h[:a], h[a:b], h[b:n] = token_seq, state_slots, selected
+        self._extra_dev[:n].copy_(self._extra_host[:n], non_blocking=True)
+        d = self._extra_dev
+        return d[:a], d[a:b], d[b:n]
+
+    # ---- one step ----
+    def execute(self, plan: StepPlan, want_residual_trace: bool = False) -> StepOutput:
+        chunks = plan.chunks
+        if not chunks:
+            return StepOutput(None, None)
+        seqs, token_seq, slots, selected, rows = [], [], [], [], []
+        t0 = 0
+        for b, c in enumerate(chunks):
+            end = c.start + c.count
+            if -(-end // self.block_size) > len(c.block_table):
+                raise AtomaError(f"sequence {c.seq.seq_id}: {end} tokens need more pages than its block table holds")
+            seqs.append(SequenceInput(np.asarray(c.seq.tokens[:end], dtype=np.uint32), num_computed_tokens=c.start,
+                                      token_chunk_size=c.count, block_table=np.asarray(c.block_table, dtype=np.uint32),
+                                      is_prompt=True))
+            token_seq.append(np.full(c.count, b, dtype=np.int32))
+            slots.append(0 if c.state_slot is None else c.state_slot)
+            for w in c.want:
+                if not 0 <= w < c.count:
+                    raise AtomaError(f"sequence {c.seq.seq_id}: wanted offset {w} outside a chunk of {c.count}")
+                selected.append(t0 + w)
+                rows.append((c.seq.seq_id, w))
+            t0 += c.count
+        T, B, S = t0, len(chunks), len(selected)
+        lay, v = self._stager.prepare_raw(seqs)
+        if lay.num_tokens != T or lay.num_slots != T:
+            raise AtomaError(f"step inputs: {lay.num_tokens} tokens / {lay.num_slots} slots prepared for a plan of {T}")
+        tseq, sslots, sel = self._extras(np.concatenate(token_seq), np.asarray(slots, dtype=np.int32),
+                                         np.asarray(selected, dtype=np.int32))
+        self._reserve(T, S)
+        bt = v["block_tables"]
+        trace = (torch.empty((len(self.spec.layers), T, self.spec.width), dtype=torch.float32, device=self.device)
+                 if want_residual_trace else None)
+        hb = HybridBatch()
+        hb.num_tokens, hb.num_seqs, hb.num_selected, hb.max_blocks = T, B, S, bt.shape[1]
+        hb.max_query_len = max(c.count for c in chunks)
+        hb.tokens, hb.positions, hb.slot_mapping = v["tokens"].data_ptr(), v["positions"].data_ptr(), v["slot_mapping"].data_ptr()
+        hb.token_seq, hb.query_start, hb.context_lens = tseq.data_ptr(), v["query_start"].data_ptr(), v["context_lengths"].data_ptr()
+        hb.block_tables, hb.state_slots = bt.data_ptr(), sslots.data_ptr()
+        hb.selected = sel.data_ptr() if S else None
+        hb.scratch, hb.scratch_bytes = self._scratch.data_ptr(), self._scratch.numel()
+        hb.logits = self._logits.data_ptr() if S else None
+        hb.next_tokens = self._next.data_ptr() if S else None
+        hb.residual_trace = trace.data_ptr() if trace is not None else None
+        L = _lib.lib()
+        L.atoma_reset_launch_count()
+        L.atoma_hybrid_step(C.byref(self._model), C.byref(hb), torch.cuda.current_stream(self.device).cuda_stream)
+        if L.atoma_last_status() != 0:
+            raise AtomaError(L.atoma_last_error().decode())
+        self.launches_last_step = int(L.atoma_launch_count())
+        return StepOutput(self._logits[:S] if S else None, self._next[:S] if S else None, rows, trace)
+
+
+def slopes_power_of_two(heads: int, exponent: float = 8.0) -> List[float]:
+    """Distance slopes 2^(-exponent (h + 1) / heads), h = 0 .. heads - 1."""
+    return [2.0 ** (-exponent * (h + 1) / heads) for h in range(heads)]

@@ -153,7 +153,8 @@ class InputStager:
             self._events[self._turn] = ev
         return lay
 
-    def _views(self, lay: ModelInputLayout, prefix_caching: bool) -> ModelInput:
+    def raw_views(self, lay: ModelInputLayout) -> dict:
+        """The step's tensors as views of the device image, by name (what `ModelInput` wraps)."""
         d = self._dev
 
         def view(off, count, dtype):
@@ -161,19 +162,30 @@ class InputStager:
             return d[off: off + count * item].view(dtype)
 
         B = lay.num_sequences
-        tokens = view(lay.input_tokens_off, lay.num_tokens, torch.int32)
-        positions = view(lay.input_positions_off, lay.num_tokens, torch.int64)
-        slots = view(lay.slot_mapping_off, lay.num_slots, torch.int64)
-        seq_lens = view(lay.sequence_lengths_off, B, torch.int32)
-        ctx_lens = view(lay.context_lengths_off, B, torch.int32)
-        seq_start = view(lay.sequence_start_loc_off, B + 1, torch.int32)
-        query_start = view(lay.query_start_loc_off, B + 1, torch.int32)
-        tables = view(lay.block_tables_off, B * lay.max_block_table_len, torch.int32).reshape(B, lay.max_block_table_len)
-        md = FlashAttentionMetadata.new(ctx_lens, slots, query_start, lay.num_prefill_tokens, lay.num_decode_tokens,
-                                        lay.max_query_len, lay.max_decode_seq_len, lay.max_prefill_seq_len,
-                                        lay.num_prefills, seq_start, seq_lens, tables, prefix_caching)
-        return ModelInput(tokens.unsqueeze(0), positions.unsqueeze(0), lay.num_decode_tokens, lay.num_prefills,
-                          query_start, md, lay)
+        return {
+            "tokens": view(lay.input_tokens_off, lay.num_tokens, torch.int32),
+            "positions": view(lay.input_positions_off, lay.num_tokens, torch.int64),
+            "slot_mapping": view(lay.slot_mapping_off, lay.num_slots, torch.int64),
+            "sequence_lengths": view(lay.sequence_lengths_off, B, torch.int32),
+            "context_lengths": view(lay.context_lengths_off, B, torch.int32),
+            "sequence_start": view(lay.sequence_start_loc_off, B + 1, torch.int32),
+            "query_start": view(lay.query_start_loc_off, B + 1, torch.int32),
+            "block_tables": view(lay.block_tables_off, B * lay.max_block_table_len, torch.int32).reshape(B, lay.max_block_table_len),
+        }
+
+    def prepare_raw(self, seqs: Seq_[SequenceInput]):
+        """(layout, views by name) of a step — for executors that take the tensors directly (mixed batches of
+        prompt portions and decoded tokens: call with enable_chunked_prefill so that every sequence has a block table)."""
+        lay = self._fill(self._marshal(seqs), allow_grow=True)
+        return lay, self.raw_views(lay)
+
+    def _views(self, lay: ModelInputLayout, prefix_caching: bool) -> ModelInput:
+        v = self.raw_views(lay)
+        md = FlashAttentionMetadata.new(v["context_lengths"], v["slot_mapping"], v["query_start"], lay.num_prefill_tokens,
+                                        lay.num_decode_tokens, lay.max_query_len, lay.max_decode_seq_len, lay.max_prefill_seq_len,
+                                        lay.num_prefills, v["sequence_start"], v["sequence_lengths"], v["block_tables"], prefix_caching)
+        return ModelInput(v["tokens"].unsqueeze(0), v["positions"].unsqueeze(0), lay.num_decode_tokens, lay.num_prefills,
+                          v["query_start"], md, lay)
 
 
 def compute_selected_token_indices(cumulative_query_lengths: torch.Tensor) -> torch.Tensor:
