@@ -151,10 +151,11 @@ class DecodeBatch(C.Structure):
 class SigmoidAttnArgs(C.Structure):
     """struct atoma_sigmoid_attn_args (include/atoma_hybrid.h)"""
 
-    _fields_ = ([(n, C.c_void_p) for n in ("q", "k_cache", "v_cache", "out", "positions", "token_seq", "block_tables",
+    _fields_ = ([(n, C.c_void_p) for n in ("q", "k_cache", "v_cache", "out", "positions", "token_seq", "query_start", "block_tables",
                                            "slopes", "head_bias", "talk")] +
                 [(n, C.c_int64) for n in ("T", "B", "max_blocks", "H", "G", "dim", "vdim", "block_size")] +
-                [("scale", C.c_float), ("softcap", C.c_float), ("dtype", C.c_uint32), ("max_query_len", C.c_int32)])
+                [("scale", C.c_float), ("softcap", C.c_float), ("dtype", C.c_uint32), ("max_query_len", C.c_int32),
+                 ("max_seq_len", C.c_int32)])
 
 
 class HybridLayer(C.Structure):
@@ -184,7 +185,7 @@ class HybridBatch(C.Structure):
     """struct atoma_hybrid_batch"""
 
     _fields_ = ([(n, C.c_int64) for n in ("num_tokens", "num_seqs", "num_selected", "max_blocks")] +
-                [("max_query_len", C.c_int32)] +
+                [("max_query_len", C.c_int32), ("max_seq_len", C.c_int32)] +
                 [(n, C.c_void_p) for n in ("tokens", "positions", "slot_mapping", "token_seq", "query_start", "context_lens",
                                            "block_tables", "state_slots", "selected", "scratch")] +
                 [("scratch_bytes", C.c_int64)] +
@@ -258,6 +259,7 @@ SIGNATURES = {
     "atoma_qkv_rope_cache": (None, [C.c_void_p] * 3 + [C.c_int64] * 8 + [C.c_void_p] * 3 + [C.c_int64] +
                              [C.c_void_p] * 3 + [C.c_int64] * 2 + [C.c_uint32, C.c_void_p]),
     "atoma_gate_up_silu": (None, [C.c_void_p] * 3 + [C.c_int64] * 6 + [C.c_uint32, C.c_void_p]),
+    "atoma_gate_up_act": (None, [C.c_void_p] * 3 + [C.c_int64] * 6 + [C.c_int32, C.c_uint32, C.c_void_p]),
     "atoma_add_rmsnorm": (None, [C.c_void_p] * 5 + [C.c_int64] * 6 + [C.c_float, C.c_uint32, C.c_void_p]),
     "atoma_embedding": (None, [C.c_void_p] * 3 + [C.c_int64] * 5 + [C.c_uint32, C.c_void_p]),
     "atoma_sample_greedy": (None, [C.c_void_p] + [C.c_int64] * 3 + [C.c_uint32] + [C.c_void_p] * 3 +

@@ -270,7 +270,13 @@ __device__ __forceinline__ void epilogue_tile(const SkinnyArgs &a, const EpiRow<
                 // silu(gate) * up (llama.rs:364): fp32 on the model-dtype projections, one rounding
                 float o[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) o[i] = (f1[i] / (1.f + __expf(-f1[i]))) * f2[i];
+                for (int i = 0; i < 8; ++i) {
+                    float gate;
+                    if (a.glu_act == 1) gate = fmaxf(f1[i], 0.f);
+                    else if (a.glu_act == 2) gate = 0.5f * f1[i] * (1.f + tanhf(0.7978845608028654f * (f1[i] + 0.044715f * f1[i] * f1[i] * f1[i])));
+                    else gate = f1[i] / (1.f + __expf(-f1[i]));
+                    o[i] = gate * f2[i];
+                }
                 store8<T>(y + j0, pack8<T>(o), J - j0, y_vec);
             } else {
                 // RoPE (non-interleaved, candle_nn::rotary_emb::rope; llama.rs:218-251) on q and k heads;

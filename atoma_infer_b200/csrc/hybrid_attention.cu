@@ -1,17 +1,259 @@
-// Sigmoid attention over a paged cache: the tensor-core kernel for portions of prompts and the split
-// kernel for single decoded tokens (include/atoma_hybrid.h).
+// Sigmoid attention over a paged cache, tensor-core kernel for portions of prompts (include/atoma_hybrid.h).
+//
+// A CTA owns 16 consecutive query tokens of one sequence and ALL heads: warp h computes head h.  The talking-heads
+// mix needs every head's weight of a (query, key) pair before any head can apply it, so the CTA walks the keys in
+// tiles of 32 and, per tile,
+//   1. stages the tile's keys and values of every kv head in shared memory (cp.async through the block table; rows
+//      past the sequence's end are zero-filled so that a masked weight never multiplies stale page contents),
+//   2. warp h: S_h = Q_h K^T on mma.sync m16n8k16 (bf16 in, float32 out), then scale, soft cap, distance bias, head
+//      bias and sigmoid in float32, causal mask as an exact zero, weights to shared memory as float32,
+//   3. warp h: a'_h = sum_g talk[h, g] a_g in float32 straight into the A fragments of the second product,
+//      O_h += a'_h V (bf16 in, float32 accumulators in registers).
+// There is no softmax, hence no running maximum and no rescaling: tiles simply add, in position order.
+// Tiles entirely behind the causal frontier are never visited.  Single decoded tokens of a mixed batch ride along as
+// one-row tiles; decode-only batches take the split kernel of hybrid_ops.cu instead.
+//
+// Why mma.sync and not tcgen05 here: the M extent a CTA can offer is 16 query rows per head before the per-head
+// float32 weights of a tile (H x rows x keys) outgrow shared memory, and the weight mix between the two products
+// runs on CUDA cores; a 128-row tcgen05 tile per head would need the weights of all heads resident in tensor memory
+// at once (H x 32 columns per 32 keys) with a tcgen05.ld / st round trip for the mix.
 #include "common.cuh"
 #include "hybrid_common.cuh"
 
 #include "atoma_hybrid.h"
 
-namespace atoma {
+#include <algorithm>
 
+namespace atoma {
+namespace {
+
+using namespace hybrid;
+
+constexpr int kPfRows = 16, kPfKeys = 32, kPfPStride = kPfKeys + 8;
+
+struct PfLayout {
+    int k_off, v_off, p_off, talk_off, bias_off, slope_off, total;
+};
+
+__host__ __device__ inline PfLayout pf_layout(int H, int G, int D, int DV) {
+    PfLayout l;
+    int off = 0;
+    l.k_off = off;
+    off += G * kPfKeys * (D + 8) * 2;
+    l.v_off = off;
+    off += G * kPfKeys * (DV + 8) * 2;
+    l.p_off = off;
+    off += H * kPfRows * kPfPStride * 4;
+    l.talk_off = off;
+    off += H * H * 4;
+    l.bias_off = off;
+    off += H * 4;
+    l.slope_off = off;
+    off += H * 4;
+    l.total = off;
+    return l;
+}
+
+template <int KMAX, int MAXWARPS>
+__global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(const atoma_sigmoid_attn_args a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int H = static_cast<int>(a.H), G = static_cast<int>(a.G), D = static_cast<int>(a.dim), DV = static_cast<int>(a.vdim);
+    const int b = blockIdx.y;
+    const int t_begin = a.query_start[b], n_q = a.query_start[b + 1] - t_begin;
+    const int r0 = blockIdx.x * kPfRows;
+    if (r0 >= n_q) return;
+    const int rows = min(kPfRows, n_q - r0);
+    const int tok0 = t_begin + r0;
+    const int ctx = static_cast<int>(a.positions[t_begin]);
+    const int p0 = ctx + r0, p_last = p0 + rows - 1, total = ctx + n_q;
+    const int bs = static_cast<int>(a.block_size);
+    const int32_t *bt = a.block_tables + static_cast<int64_t>(b) * a.max_blocks;
+    const int h = threadIdx.x >> 5, lane = threadIdx.x & 31, t4 = lane & 3, rq = lane >> 2;
+    const int c = h / (H / G);
+    const int nthreads = blockDim.x;
+    const PfLayout L = pf_layout(H, G, D, DV);
+    __nv_bfloat16 *Ks = reinterpret_cast<__nv_bfloat16 *>(smem + L.k_off);
+    __nv_bfloat16 *Vs = reinterpret_cast<__nv_bfloat16 *>(smem + L.v_off);
+    float *Ps = reinterpret_cast<float *>(smem + L.p_off);
+    float *talk_s = reinterpret_cast<float *>(smem + L.talk_off);
+    float *bias_s = reinterpret_cast<float *>(smem + L.bias_off);
+    float *slope_s = reinterpret_cast<float *>(smem + L.slope_off);
+    for (int i = threadIdx.x; i < H * H; i += nthreads) talk_s[i] = a.talk ? a.talk[i] : ((i / H == i % H) ? 1.f : 0.f);
+    for (int i = threadIdx.x; i < H; i += nthreads) {
+        bias_s[i] = a.head_bias[i];
+        slope_s[i] = a.slopes[i];
+    }
+    const __nv_bfloat16 *kc = static_cast<const __nv_bfloat16 *>(a.k_cache);
+    const __nv_bfloat16 *vc = static_cast<const __nv_bfloat16 *>(a.v_cache);
+
+    // this warp's query fragments (A operand of m16n8k16: rows rq / rq + 8, k = 2 t4 .. + 1 and + 8)
+    uint32_t qf[KMAX / 16][4];
+    {
+        const __nv_bfloat16 *q = static_cast<const __nv_bfloat16 *>(a.q) + static_cast<int64_t>(tok0) * H * D + h * D;
+#pragma unroll
+        for (int kk = 0; kk < KMAX / 16; ++kk) {
+            qf[kk][0] = qf[kk][1] = qf[kk][2] = qf[kk][3] = 0u;
+            if (kk * 16 < D) {
+                const int col = kk * 16 + 2 * t4;
+                if (rq < rows) {
+                    qf[kk][0] = *reinterpret_cast<const uint32_t *>(q + static_cast<int64_t>(rq) * H * D + col);
+                    qf[kk][2] = *reinterpret_cast<const uint32_t *>(q + static_cast<int64_t>(rq) * H * D + col + 8);
+                }
+                if (rq + 8 < rows) {
+                    qf[kk][1] = *reinterpret_cast<const uint32_t *>(q + static_cast<int64_t>(rq + 8) * H * D + col);
+                    qf[kk][3] = *reinterpret_cast<const uint32_t *>(q + static_cast<int64_t>(rq + 8) * H * D + col + 8);
+                }
+            }
+        }
+    }
+    float o[KMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < KMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    const int ck = G * D / 8, cv = G * DV / 8;   // 16-byte pieces per cache row
+    __syncthreads();
+    const float slope = slope_s[h], hb = bias_s[h];
+
+    for (int j0 = 0; j0 <= p_last; j0 += kPfKeys) {
+        // 1. stage keys and values
+        for (int i = threadIdx.x; i < kPfKeys * ck; i += nthreads) {
+            const int jj = i / ck, e = i % ck, j = j0 + jj;
+            const bool ok = j < total;
+            const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
+            const int g = (e * 8) / D, d = (e * 8) % D;
+            cp_async_16(smem_u32(Ks + (g * kPfKeys + jj) * (D + 8) + d), kc + slot * G * D + e * 8, ok ? 16 : 0);
+        }
+        for (int i = threadIdx.x; i < kPfKeys * cv; i += nthreads) {
+            const int jj = i / cv, e = i % cv, j = j0 + jj;
+            const bool ok = j < total;
+            const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
+            const int g = (e * 8) / DV, d = (e * 8) % DV;
+            cp_async_16(smem_u32(Vs + (g * kPfKeys + jj) * (DV + 8) + d), vc + slot * G * DV + e * 8, ok ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait_all();
+        __syncthreads();
+
+        // 2. scores and weights of this warp's head
+        float sacc[kPfKeys / 8][4];
+#pragma unroll
+        for (int i = 0; i < kPfKeys / 8; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < KMAX / 16; ++kk) {
+            if (kk * 16 < D) {
+#pragma unroll
+                for (int np = 0; np < kPfKeys / 16; ++np) {
+                    uint32_t r[4];
+                    const __nv_bfloat16 *src = Ks + (c * kPfKeys + (np * 2 + (lane >> 4)) * 8 + (lane & 7)) * (D + 8) + kk * 16 +
+                                               ((lane >> 3) & 1) * 8;
+                    ldmatrix_x4(r, smem_u32(src));
+                    Mma16816<__nv_bfloat16>::run(sacc[np * 2], qf[kk], r[0], r[1]);
+                    Mma16816<__nv_bfloat16>::run(sacc[np * 2 + 1], qf[kk], r[2], r[3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < kPfKeys / 8; ++nt) {
+            float w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = rq + (e >> 1) * 8, j = j0 + nt * 8 + 2 * t4 + (e & 1), p = p0 + row;
+                w[e] = (row < rows && j <= p) ? sigmoid_weight(sacc[nt][e], a.scale, a.softcap, slope, static_cast<float>(p - j), hb) : 0.f;
+            }
+            float *dst = Ps + (h * kPfRows + rq) * kPfPStride + nt * 8 + 2 * t4;
+            *reinterpret_cast<float2 *>(dst) = make_float2(w[0], w[1]);
+            *reinterpret_cast<float2 *>(dst + 8 * kPfPStride) = make_float2(w[2], w[3]);
+        }
+        __syncthreads();
+
+        // 3. mix the heads' weights and apply them to this warp's values
+#pragma unroll
+        for (int kk = 0; kk < kPfKeys / 16; ++kk) {
+            float m[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m[i] = 0.f;
+            for (int g = 0; g < H; ++g) {
+                const float tg = talk_s[h * H + g];
+                const float *src = Ps + (g * kPfRows + rq) * kPfPStride + kk * 16 + 2 * t4;
+                const float2 x0 = *reinterpret_cast<const float2 *>(src);
+                const float2 x1 = *reinterpret_cast<const float2 *>(src + 8 * kPfPStride);
+                const float2 x2 = *reinterpret_cast<const float2 *>(src + 8);
+                const float2 x3 = *reinterpret_cast<const float2 *>(src + 8 * kPfPStride + 8);
+                m[0] = fmaf(tg, x0.x, m[0]);
+                m[1] = fmaf(tg, x0.y, m[1]);
+                m[2] = fmaf(tg, x1.x, m[2]);
+                m[3] = fmaf(tg, x1.y, m[3]);
+                m[4] = fmaf(tg, x2.x, m[4]);
+                m[5] = fmaf(tg, x2.y, m[5]);
+                m[6] = fmaf(tg, x3.x, m[6]);
+                m[7] = fmaf(tg, x3.y, m[7]);
+            }
+            uint32_t af[4];
+            af[0] = pack2<__nv_bfloat16>(m[0], m[1]);
+            af[1] = pack2<__nv_bfloat16>(m[2], m[3]);
+            af[2] = pack2<__nv_bfloat16>(m[4], m[5]);
+            af[3] = pack2<__nv_bfloat16>(m[6], m[7]);
+#pragma unroll
+            for (int n2 = 0; n2 < KMAX / 16; ++n2) {
+                if (n2 * 16 < DV) {
+                    uint32_t r[4];
+                    const __nv_bfloat16 *src = Vs + (c * kPfKeys + kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * (DV + 8) + n2 * 16 +
+                                               (lane >> 4) * 8;
+                    ldmatrix_x4_trans(r, smem_u32(src));
+                    Mma16816<__nv_bfloat16>::run(o[n2 * 2], af, r[0], r[1]);
+                    Mma16816<__nv_bfloat16>::run(o[n2 * 2 + 1], af, r[2], r[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(a.out) + static_cast<int64_t>(tok0) * H * DV + h * DV;
+#pragma unroll
+    for (int nt = 0; nt < KMAX / 8; ++nt) {
+        if (nt * 8 < DV) {
+            const int col = nt * 8 + 2 * t4;
+            if (rq < rows) *reinterpret_cast<uint32_t *>(out + static_cast<int64_t>(rq) * H * DV + col) = pack2<__nv_bfloat16>(o[nt][0], o[nt][1]);
+            if (rq + 8 < rows)
+                *reinterpret_cast<uint32_t *>(out + static_cast<int64_t>(rq + 8) * H * DV + col) = pack2<__nv_bfloat16>(o[nt][2], o[nt][3]);
+        }
+    }
+}
+
+template <int KMAX, int MAXWARPS>
+cudaError_t launch_prefill(const atoma_sigmoid_attn_args &a, size_t smem_bytes, cudaStream_t stream) {
+    static int attr_dev = -1;
+    const int dev = current_device_info().ordinal;
+    if (attr_dev != dev) {
+        cudaFuncSetAttribute(sigmoid_attn_prefill_kernel<KMAX, MAXWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_dev = dev;
+    }
+    const dim3 grid(static_cast<unsigned>((a.max_query_len + kPfRows - 1) / kPfRows), static_cast<unsigned>(a.B));
+    return launch_ex(sigmoid_attn_prefill_kernel<KMAX, MAXWARPS>, grid, dim3(static_cast<unsigned>(32 * a.H)), smem_bytes, stream, a);
+}
+
+}  // namespace
+
+// Takes the batch when it holds a portion longer than one token, in bfloat16, with head sizes the tiles cover.
 bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, bool *taken) {
-    (void)a;
-    (void)stream;
     *taken = false;
-    return true;
+    const int64_t kmax = std::max(a.dim, a.vdim);
+    auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (a.dtype != ATOMA_DTYPE_BF16 || a.max_query_len <= 1 || !a.query_start || a.dim % 16 || a.vdim % 16 || kmax > 128 ||
+        a.H > (kmax <= 64 ? 16 : 8) || !al(a.q) || !al(a.k_cache) || !al(a.v_cache) || !al(a.out) ||
+        current_device_info().cc_major < 8)
+        return true;
+    const PfLayout L = pf_layout(static_cast<int>(a.H), static_cast<int>(a.G), static_cast<int>(a.dim), static_cast<int>(a.vdim));
+    if (L.total > 200 * 1024) return true;
+    *taken = true;
+    const cudaError_t e = kmax <= 64 ? launch_prefill<64, 16>(a, L.total, stream) : launch_prefill<128, 8>(a, L.total, stream);
+    note_launch();
+    if (e != cudaSuccess) {
+        set_status(static_cast<int>(e), "sigmoid_attn_prefill_kernel: %s", cudaGetErrorString(e));
+        return false;
+    }
+    return check_launch("sigmoid_attn_prefill_kernel");
 }
 
 }  // namespace atoma

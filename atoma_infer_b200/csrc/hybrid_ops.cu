@@ -139,14 +139,39 @@ __global__ void __launch_bounds__(kRowThreads) qk_norm_cache_kernel(const T *__r
 }
 
 // ---------------------------------------------------------------------------------------------
-// sigmoid attention, general kernel: one CTA per query token, keys in position order
+// sigmoid attention, general kernel: one CTA per (query token, key split), keys in position order.
+// With splits > 1 (decode steps over long contexts: few query tokens, many keys) every CTA writes the float32
+// partial sums of its key range and attn_split_reduce_kernel adds them in split order — there is no softmax, so
+// partial results simply add.
 // ---------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float dot_row(const float *__restrict__ q, const T *__restrict__ k, int D) {
+    float dot = 0.f;
+    for (int d = 0; d < D; ++d) dot = fmaf(q[d], to_f(k[d]), dot);
+    return dot;
+}
+// bfloat16 rows of a multiple of 8 elements: 16-byte loads
+__device__ __forceinline__ float dot_row_vec(const float *__restrict__ q, const __nv_bfloat16 *__restrict__ k, int D) {
+    float dot = 0.f;
+    for (int d = 0; d < D; d += 8) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(k + d);
+        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            dot = fmaf(q[d + 2 * i], f.x, dot);
+            dot = fmaf(q[d + 2 * i + 1], f.y, dot);
+        }
+    }
+    return dot;
+}
 constexpr int kGenThreads = 256;
 constexpr int kGenKeys = 32;      // keys per pass
 constexpr int kGenMaxOut = 16;    // outputs per thread: H * vdim <= 4096
 
 template <typename T>
-__global__ void __launch_bounds__(kGenThreads) sigmoid_attn_general_kernel(const atoma_sigmoid_attn_args a) {
+__global__ void __launch_bounds__(kGenThreads) sigmoid_attn_general_kernel(const atoma_sigmoid_attn_args a, int splits,
+                                                                           float *__restrict__ partial) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -170,16 +195,24 @@ __global__ void __launch_bounds__(kGenThreads) sigmoid_attn_general_kernel(const
 #pragma unroll
     for (int r = 0; r < kGenMaxOut; ++r) acc[r] = 0.f;
     __syncthreads();
-    for (int j0 = 0; j0 <= p; j0 += kGenKeys) {
+    int k_lo = 0, k_hi = p + 1;
+    if (splits > 1) {
+        const int per = ((p + splits) / splits + kGenKeys - 1) / kGenKeys * kGenKeys;
+        k_lo = min(p + 1, static_cast<int>(blockIdx.y) * per);
+        k_hi = min(p + 1, k_lo + per);
+    }
+    const bool vec = sizeof(T) == 2 && D % 8 == 0;
+    for (int j0 = k_lo; j0 < k_hi; j0 += kGenKeys) {
         for (int idx = threadIdx.x; idx < H * kGenKeys; idx += kGenThreads) {
             const int g = idx / kGenKeys, j = j0 + idx % kGenKeys;
             float w = 0.f;
-            if (j <= p) {
+            if (j < k_hi) {
                 const int64_t slot = static_cast<int64_t>(bt[j / bs]) * bs + j % bs;
                 const T *kr = kc + (slot * G + g / rep) * D;
                 const float *qh = q_s + g * D;
-                float dot = 0.f;
-                for (int d = 0; d < D; ++d) dot = fmaf(qh[d], to_f(kr[d]), dot);
+                float dot;
+                if (vec) dot = dot_row_vec(qh, reinterpret_cast<const __nv_bfloat16 *>(kr), D);
+                else dot = dot_row<T>(qh, kr, D);
                 w = sigmoid_weight(dot, a.scale, a.softcap, a.slopes[g], static_cast<float>(p - j), a.head_bias[g]);
             }
             w_s[idx] = w;
@@ -192,7 +225,7 @@ __global__ void __launch_bounds__(kGenThreads) sigmoid_attn_general_kernel(const
             m_s[idx] = m;
         }
         __syncthreads();
-        const int nj = min(kGenKeys, p + 1 - j0);
+        const int nj = min(kGenKeys, k_hi - j0);
 #pragma unroll
         for (int r = 0; r < kGenMaxOut; ++r) {
             const int od = threadIdx.x + r * kGenThreads;
@@ -209,11 +242,33 @@ __global__ void __launch_bounds__(kGenThreads) sigmoid_attn_general_kernel(const
         }
         __syncthreads();
     }
+    if (partial) {
+        float *o = partial + (static_cast<int64_t>(t) * splits + blockIdx.y) * H * Dv;
+#pragma unroll
+        for (int r = 0; r < kGenMaxOut; ++r) {
+            const int od = threadIdx.x + r * kGenThreads;
+            if (od < H * Dv) o[od] = acc[r];
+        }
+        return;
+    }
     T *o = static_cast<T *>(a.out) + static_cast<int64_t>(t) * H * Dv;
 #pragma unroll
     for (int r = 0; r < kGenMaxOut; ++r) {
         const int od = threadIdx.x + r * kGenThreads;
         if (od < H * Dv) o[od] = from_f<T>(acc[r]);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) attn_split_reduce_kernel(const float *__restrict__ partial, T *__restrict__ out, int splits,
+                                                                int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float s = 0.f;
+        for (int k = 0; k < splits; ++k) s += partial[(t * splits + k) * n + i];
+        out[t * n + i] = from_f<T>(s);
     }
 }
 
@@ -501,8 +556,25 @@ bool hyb_attention_general(const atoma_sigmoid_attn_args &a, cudaStream_t stream
         cudaFuncSetAttribute(sigmoid_attn_general_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         cudaFuncSetAttribute(sigmoid_attn_general_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     }
-#define CALL(TT) launch_ex(sigmoid_attn_general_kernel<TT>, dim3(static_cast<unsigned>(a.T)), dim3(kGenThreads), smem, stream, a)
-    return finish(HYB_DISPATCH(a.dtype, CALL), "sigmoid_attn_general_kernel");
+    // decode-only batches over long contexts: split the keys so that the few query tokens fill the device
+    int splits = 1;
+    if (a.max_query_len == 1 && a.max_seq_len >= 4 * kGenKeys && !(g_hybrid_debug & 2)) {
+        const int64_t want = (2 * current_device_info().sm_count + a.T - 1) / a.T;
+        splits = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({want, (a.max_seq_len + 2 * kGenKeys - 1) / (2 * kGenKeys), 64})));
+    }
+    float *partial = nullptr;
+    if (splits > 1) {
+        partial = static_cast<float *>(get_workspace(stream, static_cast<size_t>(a.T) * splits * a.H * a.vdim * 4, kWorkspaceHybridAttn));
+        if (!partial) return false;
+    }
+    const dim3 grid(static_cast<unsigned>(a.T), static_cast<unsigned>(splits));
+#define CALL(TT) launch_ex(sigmoid_attn_general_kernel<TT>, grid, dim3(kGenThreads), smem, stream, a, splits, partial)
+    if (!finish(HYB_DISPATCH(a.dtype, CALL), "sigmoid_attn_general_kernel")) return false;
+#undef CALL
+    if (splits == 1) return true;
+#define CALL(TT) launch_ex(attn_split_reduce_kernel<TT>, dim3(static_cast<unsigned>(a.T)), dim3(256), 0, stream, partial, \
+                           static_cast<TT *>(a.out), splits, static_cast<int>(a.H * a.vdim))
+    return finish(HYB_DISPATCH(a.dtype, CALL), "attn_split_reduce_kernel");
 #undef CALL
 }
 
@@ -580,6 +652,13 @@ bool hyb_linear(const void *x, const void *w, void *y, int64_t T, int64_t N, int
 // gate/up projection + gated activation: act_out[T, ff] = act(x Wg^T) * (x Wu^T), w_gate_up = [Wg; Wu].
 bool hyb_gate_up_act(const void *x, const void *w_gate_up, void *proj, void *act_out, int64_t T, int64_t ff, int64_t K, int32_t act,
                      uint32_t dtype, cudaStream_t stream) {
+    auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    // decode-sized steps in bfloat16: the activation runs in the projection's epilogue (the tile pairs gate row i with up row i)
+    if (dtype == ATOMA_DTYPE_BF16 && !(g_hybrid_debug & 1) && T <= 128 && K % 64 == 0 && ff % 8 == 0 && al(x) && al(w_gate_up) &&
+        al(act_out) && current_device_info().cc_major == 10) {
+        atoma_gate_up_act(x, w_gate_up, act_out, T, ff, K, K, K, ff, act, 1, stream);
+        return atoma_last_status() == 0;
+    }
     if (!hyb_linear(x, w_gate_up, proj, T, 2 * ff, K, dtype, stream)) return false;
     return hyb_glu(proj, act_out, T, ff, act, dtype, stream);
 }

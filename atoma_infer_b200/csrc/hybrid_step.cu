@@ -157,6 +157,8 @@ extern "C" void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_h
             a.out = s.act;
             a.positions = b.positions;
             a.token_seq = b.token_seq;
+            a.query_start = b.query_start;
+            a.max_seq_len = b.max_seq_len;
             a.block_tables = b.block_tables;
             a.slopes = l.slopes;
             a.head_bias = l.head_bias;

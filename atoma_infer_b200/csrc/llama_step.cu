@@ -150,7 +150,7 @@ bool qkv_rope_cache(const void *x, const void *wqkv, void *qkv, int64_t T, int64
 }
 
 bool gate_up_silu(const void *x, const void *w, void *y, int64_t T, int64_t inter, int64_t K, int64_t ldx, int64_t ldw,
-                  int64_t ldy, uint32_t dtype, cudaStream_t stream) {
+                  int64_t ldy, uint32_t dtype, cudaStream_t stream, int act = 0) {
     if (T <= 0 || inter <= 0) return true;
     if (dtype > 1 || !x || !w || !y || !al16(x) || !al16(w) || !al16(y) || ldx % 8 || ldw % 8 || ldy % 8 || ldx < K ||
         ldw < K || ldy < inter || inter % 8) {
@@ -166,6 +166,7 @@ bool gate_up_silu(const void *x, const void *w, void *y, int64_t T, int64_t inte
         const int tn = static_cast<int>(std::min<int64_t>(128, T - t0));
         SkinnyArgs a{};
         a.epi = kEpiSilu;
+        a.glu_act = act;
         a.y = static_cast<char *>(y) + t0 * ldy * 2;
         a.ldy = ldy;
         if (!launch_skinny_gemm(a, static_cast<const char *>(x) + t0 * ldx * 2, w, tn, K, ldx, ldw, 1,
@@ -285,6 +286,16 @@ extern "C" void atoma_gate_up_silu(const void *x, const void *w_gate_up, void *y
                                    int64_t ldx, int64_t ldw, int64_t ldy, uint32_t dtype, atoma_stream_t stream) {
     clear_status();
     gate_up_silu(x, w_gate_up, y, T, inter, K, ldx, ldw, ldy, dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" void atoma_gate_up_act(const void *x, const void *w_gate_up, void *y, int64_t T, int64_t inter, int64_t K,
+                                  int64_t ldx, int64_t ldw, int64_t ldy, int32_t act, uint32_t dtype, atoma_stream_t stream) {
+    clear_status();
+    if (act < 0 || act > 2) {
+        set_status(kErrInvalidArg, "atoma_gate_up_act: activation %d (0 = silu, 1 = relu, 2 = gelu)", act);
+        return;
+    }
+    gate_up_silu(x, w_gate_up, y, T, inter, K, ldx, ldw, ldy, dtype, static_cast<cudaStream_t>(stream), act);
 }
 
 extern "C" void atoma_add_rmsnorm(const void *x, const void *residual, void *residual_out, const void *weight,

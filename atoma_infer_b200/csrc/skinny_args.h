@@ -13,7 +13,7 @@ namespace atoma {
 enum : int {
     kEpiPlain = 0,  // y[t, n] = acc
     kEpiRope = 1,   // qkv projection: RoPE on q/k heads, store to y, scatter k/v to the paged cache (f1)
-    kEpiSilu = 2,   // gate_up projection: y[t, j] = silu(gate_j) * up_j (f3)
+    kEpiSilu = 2,   // gate_up projection: y[t, j] = act(gate_j) * up_j, act = SkinnyArgs::glu_act (silu by default) (f3)
     kEpiPush = 3,   // row-parallel projection under tensor parallelism: push the addend to every rank (f4)
 };
 
@@ -30,6 +30,7 @@ struct SkinnyArgs {
     int acc_stride, tmem_cols, nacc;   // TMEM columns between accumulators, allocation, independent accumulators per tile
     int nbuf;                          // accumulator buffers (2: a tile's epilogue overlaps the next tile's MMAs; 1)
     int prefetch_w, is_bf16, epi;
+    int glu_act;                   // kEpiSilu epilogue: gate activation, 0 = silu (Llama), 1 = relu, 2 = gelu (tanh form)
     int debug_skip;                // diagnostics: 1 = skip x loads, 2 = skip W loads (garbage results)
     int trigger_late;              // 0: release the dependent grid at kernel start; N: N stages before this CTA's last weight load
     unsigned long long *trace;     // diagnostics: [cta][4] globaltimer ns, or null

@@ -246,6 +246,7 @@ class HybridExecutor:
         hb = HybridBatch()
         hb.num_tokens, hb.num_seqs, hb.num_selected, hb.max_blocks = T, B, S, bt.shape[1]
         hb.max_query_len = max(c.count for c in chunks)
+        hb.max_seq_len = max(c.start + c.count for c in chunks)
         hb.tokens, hb.positions, hb.slot_mapping = v["tokens"].data_ptr(), v["positions"].data_ptr(), v["slot_mapping"].data_ptr()
         hb.token_seq, hb.query_start, hb.context_lens = tseq.data_ptr(), v["query_start"].data_ptr(), v["context_lengths"].data_ptr()
         hb.block_tables, hb.state_slots = bt.data_ptr(), sslots.data_ptr()

@@ -69,12 +69,14 @@ typedef struct atoma_sigmoid_attn_args {
     void *out;                    /* [T, H vdim] */
     const int64_t *positions;     /* [T] */
     const int32_t *token_seq;     /* [T] batch row of every token */
+    const int32_t *query_start;   /* [B + 1] first token of every batch row (rows are contiguous, positions ascending) */
     const int32_t *block_tables;  /* [B, max_blocks] */
     const float *slopes, *head_bias, *talk; /* [H], [H], [H, H] */
     int64_t T, B, max_blocks, H, G, dim, vdim, block_size;
     float scale, softcap;
     uint32_t dtype;
     int32_t max_query_len;        /* longest portion of the batch (1 = decode only): selects the kernel */
+    int32_t max_seq_len;          /* longest sequence (context + portion) of the batch; 0 = unknown (keys are not split) */
 } atoma_sigmoid_attn_args;
 void atoma_sigmoid_attention_paged(const atoma_sigmoid_attn_args *args, atoma_stream_t stream);
 
@@ -143,7 +145,7 @@ typedef struct atoma_hybrid_model {
 
 typedef struct atoma_hybrid_batch {
     int64_t num_tokens, num_seqs, num_selected, max_blocks;
-    int32_t max_query_len;
+    int32_t max_query_len, max_seq_len;
     const uint32_t *tokens;       /* [T] */
     const int64_t *positions;     /* [T] */
     const int64_t *slot_mapping;  /* [T] */

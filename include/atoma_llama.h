@@ -63,6 +63,10 @@ void atoma_qkv_rope_cache(const void *x, const void *wqkv, void *qkv, int64_t T,
  */
 void atoma_gate_up_silu(const void *x, const void *w_gate_up, void *y, int64_t T, int64_t inter, int64_t K,
                         int64_t ldx, int64_t ldw, int64_t ldy, uint32_t dtype, atoma_stream_t stream);
+/* The same kernel with the gate's activation as an argument: act 0 = silu (atoma_gate_up_silu), 1 = relu,
+ * 2 = gelu in its tanh form. */
+void atoma_gate_up_act(const void *x, const void *w_gate_up, void *y, int64_t T, int64_t inter, int64_t K,
+                       int64_t ldx, int64_t ldw, int64_t ldy, int32_t act, uint32_t dtype, atoma_stream_t stream);
 
 /*
  * The MLP of a block (llama.rs:362-366): act[T, inter] = silu(x w_gate^T) * (x w_up^T) and y[T, hidden] = act w_down^T.

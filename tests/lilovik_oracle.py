@@ -50,8 +50,33 @@ def query_temperature(p, coef, every):
     return 1.0 + coef * math.log(math.floor((p + 1) / every) + 1.0)
 
 
-def sigmoid_attention(w, pre, x, m, eps):
-    """x [n, width] -> [n, width].  m: the layer's mixer sizes and constants."""
+def attention_core(q, k, v, m, head_bias, talk, first_position=0):
+    """q [n, H, D] (already normed and tempered) against keys / values [t, G, D] / [t, G, Dv] of positions 0 .. t-1;
+    query r sits at position first_position + r.  Returns [n, H, Dv]."""
+    H, G, Dv = m["heads"], m["kv_heads"], v.shape[-1]
+    n, t = q.shape[0], k.shape[0]
+    slopes = distance_slopes(H)
+    cap = m.get("softcap") or 0.0
+    weight = torch.zeros((H, n, t), dtype=q.dtype)
+    i = first_position + torch.arange(n)[:, None]
+    j = torch.arange(t)[None, :]
+    for h in range(H):
+        g = h // (H // G)
+        s = (q[:, h] @ k[:, g].T) * m["scale"]
+        if cap > 0:
+            s = cap * torch.tanh(s / cap)
+        s = s - slopes[h] * (i - j).to(q.dtype)
+        a = torch.sigmoid(s + head_bias[h])
+        weight[h] = torch.where(j <= i, a, torch.zeros_like(a))
+    mixed = torch.einsum("hg,gij->hij", talk, weight)
+    out = torch.zeros((n, H, Dv), dtype=q.dtype)
+    for h in range(H):
+        out[:, h] = mixed[h] @ v[:, h // (H // G)]
+    return out
+
+
+def qkv_normed(w, pre, x, m, eps, first_position=0):
+    """Projections with biases, the whole-projection q / k norms and the query temperature."""
     H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     n = x.shape[0]
     q = x @ w[pre + "q"].T + w[pre + "q.b"]
@@ -59,26 +84,17 @@ def sigmoid_attention(w, pre, x, m, eps):
     v = x @ w[pre + "v"].T + w[pre + "v.b"]
     q = rms(q, eps) * w[pre + "q.norm"]          # over the whole projection, all heads at once
     k = rms(k, eps) * w[pre + "k.norm"]
-    temp = torch.tensor([query_temperature(p, m["q_temp"]["coef"], m["q_temp"]["every"]) for p in range(n)], dtype=x.dtype)
+    temp = torch.tensor([query_temperature(first_position + r, m["q_temp"]["coef"], m["q_temp"]["every"]) for r in range(n)],
+                        dtype=x.dtype)
     q = q * temp[:, None]
-    q, k, v = q.reshape(n, H, D), k.reshape(n, G, D), v.reshape(n, G, Dv)
-    slopes = distance_slopes(H)
-    cap = m["softcap"]
-    weight = torch.zeros((H, n, n), dtype=x.dtype)
-    for h in range(H):
-        g = h // (H // G)
-        s = (q[:, h] @ k[:, g].T) * m["scale"]
-        s = cap * torch.tanh(s / cap)
-        i = torch.arange(n)[:, None]
-        j = torch.arange(n)[None, :]
-        s = s - slopes[h] * (i - j).to(x.dtype)
-        a = torch.sigmoid(s + w[pre + "pb"][h])
-        weight[h] = torch.where(j <= i, a, torch.zeros_like(a))
-    mixed = torch.einsum("hg,gij->hij", w[pre + "talk"], weight)
-    out = torch.zeros((n, H, Dv), dtype=x.dtype)
-    for h in range(H):
-        out[:, h] = mixed[h] @ v[:, h // (H // G)]
-    return out.reshape(n, H * Dv) @ w[pre + "o"].T
+    return q.reshape(n, H, D), k.reshape(n, G, D), v.reshape(n, G, Dv)
+
+
+def sigmoid_attention(w, pre, x, m, eps):
+    """x [n, width] -> [n, width].  m: the layer's mixer sizes and constants."""
+    q, k, v = qkv_normed(w, pre, x, m, eps)
+    out = attention_core(q, k, v, m, w[pre + "pb"], w[pre + "talk"])
+    return out.reshape(x.shape[0], -1) @ w[pre + "o"].T
 
 
 def mingru(w, pre, x, state=None):
@@ -160,10 +176,10 @@ def random_weights(cfg, gen, dtype=torch.float64, round_to=torch.bfloat16):
             for nme, rows in (("q", H * D), ("k", G * D), ("v", G * Dv)):
                 w[p + "mix." + nme] = r(rows, W, scale=W ** -0.5)
                 w[p + "mix." + nme + ".b"] = r(rows, scale=0.1)
-            w[p + "mix.q.norm"] = 1.0 + r(H * D, scale=0.1)
-            w[p + "mix.k.norm"] = 1.0 + r(G * D, scale=0.1)
+            w[p + "mix.q.norm"] = (1.0 + r(H * D, scale=0.1)).to(round_to).to(dtype)
+            w[p + "mix.k.norm"] = (1.0 + r(G * D, scale=0.1)).to(round_to).to(dtype)
             w[p + "mix.talk"] = (torch.eye(H) + 0.3 * torch.randn(H, H, generator=gen)).to(round_to).to(dtype)
-            w[p + "mix.pb"] = r(H, scale=0.5) - 1.0
+            w[p + "mix.pb"] = (r(H, scale=0.5) - 1.0).to(round_to).to(dtype)
             w[p + "mix.o"] = r(W, H * Dv, scale=(H * Dv) ** -0.5)
         else:
             S = m["width"]
