@@ -10,6 +10,10 @@
 //   3. warp h: a'_h = sum_g talk[h, g] a_g in float32 straight into the A fragments of the second product,
 //      O_h += a'_h V (bf16 in, float32 accumulators in registers).
 // There is no softmax, hence no running maximum and no rescaling: tiles simply add, in position order.
+// More heads than one CTA can hold (registers: a warp keeps its head's 16 x vdim float32 outputs) are spread over the
+// CTAs of a thread-block cluster, `hpc` heads each: a CTA stages only its own kv heads, keeps its own heads' weights, and
+// reads the other CTAs' weights for the mix through distributed shared memory (ld.shared::cluster) between two cluster
+// barriers per tile.
 // Tiles entirely behind the causal frontier are never visited.  Single decoded tokens of a mixed batch ride along as
 // one-row tiles; decode-only batches take the split kernel of hybrid_ops.cu instead.
 //
@@ -35,27 +39,34 @@ struct PfLayout {
     int k_off, v_off, p_off, talk_off, bias_off, slope_off, total;
 };
 
-__host__ __device__ inline PfLayout pf_layout(int H, int G, int D, int DV) {
+// hpc = heads per CTA, gl = kv heads a CTA stages, H = all heads (the talking-heads matrix rows are kept whole)
+__host__ __device__ inline PfLayout pf_layout(int hpc, int gl, int H, int D, int DV) {
     PfLayout l;
     int off = 0;
     l.k_off = off;
-    off += G * kPfKeys * (D + 8) * 2;
+    off += gl * kPfKeys * (D + 8) * 2;
     l.v_off = off;
-    off += G * kPfKeys * (DV + 8) * 2;
+    off += gl * kPfKeys * (DV + 8) * 2;
     l.p_off = off;
-    off += H * kPfRows * kPfPStride * 4;
+    off += hpc * kPfRows * kPfPStride * 4;
     l.talk_off = off;
-    off += H * H * 4;
+    off += hpc * H * 4;
     l.bias_off = off;
-    off += H * 4;
+    off += hpc * 4;
     l.slope_off = off;
-    off += H * 4;
+    off += hpc * 4;
     l.total = off;
     return l;
 }
 
+__device__ __forceinline__ float2 ld_cluster_f2(uint32_t cluster_addr) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(cluster_addr) : "memory");
+    return v;
+}
+
 template <int KMAX, int MAXWARPS>
-__global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(const atoma_sigmoid_attn_args a) {
+__global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(const atoma_sigmoid_attn_args a, int hpc, int gl, int cs) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -70,20 +81,26 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
     const int p0 = ctx + r0, p_last = p0 + rows - 1, total = ctx + n_q;
     const int bs = static_cast<int>(a.block_size);
     const int32_t *bt = a.block_tables + static_cast<int64_t>(b) * a.max_blocks;
-    const int h = threadIdx.x >> 5, lane = threadIdx.x & 31, t4 = lane & 3, rq = lane >> 2;
-    const int c = h / (H / G);
+    const int hl = threadIdx.x >> 5, lane = threadIdx.x & 31, t4 = lane & 3, rq = lane >> 2;
+    const int rank = cs > 1 ? static_cast<int>(cluster_ctarank()) : 0;
+    const int h = rank * hpc + hl;                       // this warp's head
+    const int c_lo = (rank * hpc) / (H / G);             // first kv head this CTA stages
+    const int c = h / (H / G) - c_lo;                    // this warp's kv head among the staged ones
     const int nthreads = blockDim.x;
-    const PfLayout L = pf_layout(H, G, D, DV);
+    const PfLayout L = pf_layout(hpc, gl, H, D, DV);
     __nv_bfloat16 *Ks = reinterpret_cast<__nv_bfloat16 *>(smem + L.k_off);
     __nv_bfloat16 *Vs = reinterpret_cast<__nv_bfloat16 *>(smem + L.v_off);
     float *Ps = reinterpret_cast<float *>(smem + L.p_off);
     float *talk_s = reinterpret_cast<float *>(smem + L.talk_off);
     float *bias_s = reinterpret_cast<float *>(smem + L.bias_off);
     float *slope_s = reinterpret_cast<float *>(smem + L.slope_off);
-    for (int i = threadIdx.x; i < H * H; i += nthreads) talk_s[i] = a.talk ? a.talk[i] : ((i / H == i % H) ? 1.f : 0.f);
-    for (int i = threadIdx.x; i < H; i += nthreads) {
-        bias_s[i] = a.head_bias[i];
-        slope_s[i] = a.slopes[i];
+    for (int i = threadIdx.x; i < hpc * H; i += nthreads) {
+        const int row = rank * hpc + i / H, col = i % H;
+        talk_s[i] = a.talk ? a.talk[row * H + col] : (row == col ? 1.f : 0.f);
+    }
+    for (int i = threadIdx.x; i < hpc; i += nthreads) {
+        bias_s[i] = a.head_bias[rank * hpc + i];
+        slope_s[i] = a.slopes[rank * hpc + i];
     }
     const __nv_bfloat16 *kc = static_cast<const __nv_bfloat16 *>(a.k_cache);
     const __nv_bfloat16 *vc = static_cast<const __nv_bfloat16 *>(a.v_cache);
@@ -111,9 +128,10 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
     float o[KMAX / 8][4];
 #pragma unroll
     for (int i = 0; i < KMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    const int ck = G * D / 8, cv = G * DV / 8;   // 16-byte pieces per cache row
+    const int ck = gl * D / 8, cv = gl * DV / 8;   // 16-byte pieces per staged cache row (this CTA's kv heads)
     __syncthreads();
-    const float slope = slope_s[h], hb = bias_s[h];
+    const float slope = slope_s[hl], hb = bias_s[hl];
+    const uint32_t ps_base = smem_u32(Ps);
 
     for (int j0 = 0; j0 <= p_last; j0 += kPfKeys) {
         // 1. stage keys and values
@@ -122,14 +140,14 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
             const bool ok = j < total;
             const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
             const int g = (e * 8) / D, d = (e * 8) % D;
-            cp_async_16(smem_u32(Ks + (g * kPfKeys + jj) * (D + 8) + d), kc + slot * G * D + e * 8, ok ? 16 : 0);
+            cp_async_16(smem_u32(Ks + (g * kPfKeys + jj) * (D + 8) + d), kc + (slot * G + c_lo) * D + e * 8, ok ? 16 : 0);
         }
         for (int i = threadIdx.x; i < kPfKeys * cv; i += nthreads) {
             const int jj = i / cv, e = i % cv, j = j0 + jj;
             const bool ok = j < total;
             const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
             const int g = (e * 8) / DV, d = (e * 8) % DV;
-            cp_async_16(smem_u32(Vs + (g * kPfKeys + jj) * (DV + 8) + d), vc + slot * G * DV + e * 8, ok ? 16 : 0);
+            cp_async_16(smem_u32(Vs + (g * kPfKeys + jj) * (DV + 8) + d), vc + (slot * G + c_lo) * DV + e * 8, ok ? 16 : 0);
         }
         cp_async_commit();
         cp_async_wait_all();
@@ -161,11 +179,16 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
                 const int row = rq + (e >> 1) * 8, j = j0 + nt * 8 + 2 * t4 + (e & 1), p = p0 + row;
                 w[e] = (row < rows && j <= p) ? sigmoid_weight(sacc[nt][e], a.scale, a.softcap, slope, static_cast<float>(p - j), hb) : 0.f;
             }
-            float *dst = Ps + (h * kPfRows + rq) * kPfPStride + nt * 8 + 2 * t4;
+            float *dst = Ps + (hl * kPfRows + rq) * kPfPStride + nt * 8 + 2 * t4;
             *reinterpret_cast<float2 *>(dst) = make_float2(w[0], w[1]);
             *reinterpret_cast<float2 *>(dst + 8 * kPfPStride) = make_float2(w[2], w[3]);
         }
-        __syncthreads();
+        if (cs > 1) {
+            cluster_arrive_release();
+            cluster_wait_acquire();
+        } else {
+            __syncthreads();
+        }
 
         // 3. mix the heads' weights and apply them to this warp's values
 #pragma unroll
@@ -174,12 +197,22 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
 #pragma unroll
             for (int i = 0; i < 8; ++i) m[i] = 0.f;
             for (int g = 0; g < H; ++g) {
-                const float tg = talk_s[h * H + g];
-                const float *src = Ps + (g * kPfRows + rq) * kPfPStride + kk * 16 + 2 * t4;
-                const float2 x0 = *reinterpret_cast<const float2 *>(src);
-                const float2 x1 = *reinterpret_cast<const float2 *>(src + 8 * kPfPStride);
-                const float2 x2 = *reinterpret_cast<const float2 *>(src + 8);
-                const float2 x3 = *reinterpret_cast<const float2 *>(src + 8 * kPfPStride + 8);
+                const float tg = talk_s[hl * H + g];
+                const int off = ((g % hpc) * kPfRows + rq) * kPfPStride + kk * 16 + 2 * t4;
+                float2 x0, x1, x2, x3;
+                if (cs > 1) {
+                    const uint32_t src = mapa_shared(ps_base + off * 4, static_cast<uint32_t>(g / hpc));
+                    x0 = ld_cluster_f2(src);
+                    x1 = ld_cluster_f2(src + 8 * kPfPStride * 4);
+                    x2 = ld_cluster_f2(src + 8 * 4);
+                    x3 = ld_cluster_f2(src + (8 * kPfPStride + 8) * 4);
+                } else {
+                    const float *src = Ps + off;
+                    x0 = *reinterpret_cast<const float2 *>(src);
+                    x1 = *reinterpret_cast<const float2 *>(src + 8 * kPfPStride);
+                    x2 = *reinterpret_cast<const float2 *>(src + 8);
+                    x3 = *reinterpret_cast<const float2 *>(src + 8 * kPfPStride + 8);
+                }
                 m[0] = fmaf(tg, x0.x, m[0]);
                 m[1] = fmaf(tg, x0.y, m[1]);
                 m[2] = fmaf(tg, x1.x, m[2]);
@@ -206,7 +239,12 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
                 }
             }
         }
-        __syncthreads();
+        if (cs > 1) {            // the other CTAs have read this tile's weights before the next tile overwrites them
+            cluster_arrive_release();
+            cluster_wait_acquire();
+        } else {
+            __syncthreads();
+        }
     }
 
     __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(a.out) + static_cast<int64_t>(tok0) * H * DV + h * DV;
@@ -222,15 +260,35 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
 }
 
 template <int KMAX, int MAXWARPS>
-cudaError_t launch_prefill(const atoma_sigmoid_attn_args &a, size_t smem_bytes, cudaStream_t stream) {
+cudaError_t launch_prefill(const atoma_sigmoid_attn_args &a, int hpc, int gl, int cs, size_t smem_bytes, cudaStream_t stream) {
     static int attr_dev = -1;
     const int dev = current_device_info().ordinal;
     if (attr_dev != dev) {
         cudaFuncSetAttribute(sigmoid_attn_prefill_kernel<KMAX, MAXWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr_dev = dev;
     }
-    const dim3 grid(static_cast<unsigned>((a.max_query_len + kPfRows - 1) / kPfRows), static_cast<unsigned>(a.B));
-    return launch_ex(sigmoid_attn_prefill_kernel<KMAX, MAXWARPS>, grid, dim3(static_cast<unsigned>(32 * a.H)), smem_bytes, stream, a);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>((a.max_query_len + kPfRows - 1) / kPfRows), static_cast<unsigned>(a.B), static_cast<unsigned>(cs));
+    cfg.blockDim = dim3(static_cast<unsigned>(32 * hpc));
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (cs > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = static_cast<unsigned>(cs);
+        ++n;
+    }
+    if (launch_flags() & kLaunchPdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, sigmoid_attn_prefill_kernel<KMAX, MAXWARPS>, a, hpc, gl, cs);
 }
 
 }  // namespace
@@ -241,13 +299,28 @@ bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, b
     const int64_t kmax = std::max(a.dim, a.vdim);
     auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (a.dtype != ATOMA_DTYPE_BF16 || a.max_query_len <= 1 || !a.query_start || a.dim % 16 || a.vdim % 16 || kmax > 128 ||
-        a.H > (kmax <= 64 ? 16 : 8) || !al(a.q) || !al(a.k_cache) || !al(a.v_cache) || !al(a.out) ||
-        current_device_info().cc_major < 8)
+        !al(a.q) || !al(a.k_cache) || !al(a.v_cache) || !al(a.out) || current_device_info().cc_major < 9)
         return true;
-    const PfLayout L = pf_layout(static_cast<int>(a.H), static_cast<int>(a.G), static_cast<int>(a.dim), static_cast<int>(a.vdim));
-    if (L.total > 200 * 1024) return true;
+    // heads per CTA: the largest divisor of H that the register budget allows, with at most 8 CTAs per cluster and whole
+    // kv-head groups per CTA (or several CTAs inside one group)
+    const int H = static_cast<int>(a.H), G = static_cast<int>(a.G), rep = H / G;
+    const int maxw = kmax <= 64 ? 16 : 8;
+    int hpc = 0, gl = 0;
+    for (int cand = std::min(H, maxw); cand >= 1; --cand) {
+        if (H % cand || H / cand > 8) continue;
+        if (cand % rep != 0 && rep % cand != 0) continue;
+        const int g = cand % rep == 0 ? cand / rep : 1;
+        if (pf_layout(cand, g, H, static_cast<int>(a.dim), static_cast<int>(a.vdim)).total > 200 * 1024) continue;
+        hpc = cand;
+        gl = g;
+        break;
+    }
+    if (!hpc) return true;
+    const int cs = H / hpc;
+    const PfLayout L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim));
     *taken = true;
-    const cudaError_t e = kmax <= 64 ? launch_prefill<64, 16>(a, L.total, stream) : launch_prefill<128, 8>(a, L.total, stream);
+    const cudaError_t e = kmax <= 64 ? launch_prefill<64, 16>(a, hpc, gl, cs, L.total, stream)
+                                     : launch_prefill<128, 8>(a, hpc, gl, cs, L.total, stream);
     note_launch();
     if (e != cudaSuccess) {
         set_status(static_cast<int>(e), "sigmoid_attn_prefill_kernel: %s", cudaGetErrorString(e));

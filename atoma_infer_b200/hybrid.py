@@ -222,7 +222,9 @@ class HybridExecutor:
             end = c.start + c.count
             if -(-end // self.block_size) > len(c.block_table):
                 raise AtomaError(f"sequence {c.seq.seq_id}: {end} tokens need more pages than its block table holds")
-            seqs.append(SequenceInput(np.asarray(c.seq.tokens[:end], dtype=np.uint32), num_computed_tokens=c.start,
+            ids = np.zeros(end, dtype=np.uint32)            # only the chunk's tokens are read (positions start .. end)
+            ids[c.start:end] = c.seq.tokens[c.start:end]
+            seqs.append(SequenceInput(ids, num_computed_tokens=c.start,
                                       token_chunk_size=c.count, block_table=np.asarray(c.block_table, dtype=np.uint32),
                                       is_prompt=True))
             token_seq.append(np.full(c.count, b, dtype=np.int32))
@@ -261,7 +263,18 @@ class HybridExecutor:
         if L.atoma_last_status() != 0:
             raise AtomaError(L.atoma_last_error().decode())
         self.launches_last_step = int(L.atoma_launch_count())
+        self._last = (hb, tseq, sslots, sel, trace)
         return StepOutput(self._logits[:S] if S else None, self._next[:S] if S else None, rows, trace)
+
+
+def relaunch_last_step(ex: "HybridExecutor") -> None:
+    """Enqueues the previous step's kernels again on the current stream with the inputs still on the device (timing and
+    CUDA-graph capture of a step: `torch.cuda.graph` around this call).  Recurrent state advances again; everything else
+    is rewritten with the same values."""
+    L = _lib.lib()
+    L.atoma_hybrid_step(C.byref(ex._model), C.byref(ex._last[0]), torch.cuda.current_stream(ex.device).cuda_stream)
+    if L.atoma_last_status() != 0:
+        raise AtomaError(L.atoma_last_error().decode())
 
 
 def slopes_power_of_two(heads: int, exponent: float = 8.0) -> List[float]:

@@ -132,7 +132,8 @@ def _paged_batch(g, seqs, H, G, D, Dv, bs, dtype, scale_q=1.0, k_zero_dim=None):
             dev(torch.tensor(tseq, dtype=torch.int32)), dev(bt), ref)
 
 
-ATTN_SHAPES = [(4, 2, 16, 24), (4, 4, 32, 32), (6, 1, 8, 16), (2, 2, 64, 64), (8, 4, 96, 96), (3, 3, 20, 12)]
+ATTN_SHAPES = [(4, 2, 16, 24), (4, 4, 32, 32), (6, 1, 8, 16), (2, 2, 64, 64), (8, 4, 96, 96), (3, 3, 20, 12),
+               (32, 8, 64, 64), (16, 2, 128, 128), (12, 4, 32, 48), (32, 32, 128, 96)]   # the last rows spread heads over a cluster
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
