@@ -33,22 +33,22 @@ namespace {
 
 using namespace hybrid;
 
-constexpr int kPfRows = 16, kPfKeys = 32, kPfPStride = kPfKeys + 8;
+constexpr int kPfRows = 16, kPfKeys = 32, kPfPStride = kPfKeys + 4;   // +4: a two-way bank conflict at most, and two CTAs fit an SM at 32 heads
 
 struct PfLayout {
     int k_off, v_off, p_off, talk_off, bias_off, slope_off, total;
 };
 
 // hpc = heads per CTA, gl = kv heads a CTA stages, H = all heads (the talking-heads matrix rows are kept whole)
-__host__ __device__ inline PfLayout pf_layout(int hpc, int gl, int H, int D, int DV) {
+__host__ __device__ inline PfLayout pf_layout(int hpc, int gl, int H, int D, int DV, int stages) {
     PfLayout l;
     int off = 0;
     l.k_off = off;
-    off += gl * kPfKeys * (D + 8) * 2;
+    off += stages * gl * kPfKeys * (D + 8) * 2;
     l.v_off = off;
-    off += gl * kPfKeys * (DV + 8) * 2;
+    off += stages * gl * kPfKeys * (DV + 8) * 2;
     l.p_off = off;
-    off += hpc * kPfRows * kPfPStride * 4;
+    off += H * kPfRows * kPfPStride * 4;   // every head's weights of the tile: own heads computed here, the rest copied in
     l.talk_off = off;
     off += hpc * H * 4;
     l.bias_off = off;
@@ -59,21 +59,33 @@ __host__ __device__ inline PfLayout pf_layout(int hpc, int gl, int H, int D, int
     return l;
 }
 
-__device__ __forceinline__ float2 ld_cluster_f2(uint32_t cluster_addr) {
-    float2 v;
-    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(cluster_addr) : "memory");
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(cluster_addr));
     return v;
 }
 
+// The weight of one visible key with fast exponentials (ex2.approx + one Newton-free reciprocal): tanh(x) = 1 - 2 / (e^2x + 1).
+// Relative error ~1e-6 of the weight — three orders below the bfloat16 rounding the weight gets before the second product.
+__device__ __forceinline__ float sigmoid_weight_fast(float dot, float scale, float softcap, float inv_cap, float slope, float dist,
+                                                     float head_bias) {
+    float s = dot * scale;
+    if (softcap > 0.f) s = softcap * (1.f - __fdividef(2.f, __expf(2.f * s * inv_cap) + 1.f));
+    s = s - slope * dist + head_bias;
+    return __fdividef(1.f, 1.f + __expf(-s));
+}
+
 template <int KMAX, int MAXWARPS>
-__global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(const atoma_sigmoid_attn_args a, int hpc, int gl, int cs) {
+__global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(const atoma_sigmoid_attn_args a, int hpc, int gl, int cs, int splits,
+                                                                             float *__restrict__ partial, int stages) {
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
     const int H = static_cast<int>(a.H), G = static_cast<int>(a.G), D = static_cast<int>(a.dim), DV = static_cast<int>(a.vdim);
     const int b = blockIdx.y;
     const int t_begin = a.query_start[b], n_q = a.query_start[b + 1] - t_begin;
-    const int r0 = blockIdx.x * kPfRows;
+    // splits > 1 (decode-only batches: one query row per sequence): blockIdx.x is the key split, not the query tile
+    const int r0 = splits > 1 ? 0 : blockIdx.x * kPfRows;
     if (r0 >= n_q) return;
     const int rows = min(kPfRows, n_q - r0);
     const int tok0 = t_begin + r0;
@@ -87,9 +99,10 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
     const int c_lo = (rank * hpc) / (H / G);             // first kv head this CTA stages
     const int c = h / (H / G) - c_lo;                    // this warp's kv head among the staged ones
     const int nthreads = blockDim.x;
-    const PfLayout L = pf_layout(hpc, gl, H, D, DV);
-    __nv_bfloat16 *Ks = reinterpret_cast<__nv_bfloat16 *>(smem + L.k_off);
-    __nv_bfloat16 *Vs = reinterpret_cast<__nv_bfloat16 *>(smem + L.v_off);
+    const PfLayout L = pf_layout(hpc, gl, H, D, DV, stages);
+    __nv_bfloat16 *Ks0 = reinterpret_cast<__nv_bfloat16 *>(smem + L.k_off);
+    __nv_bfloat16 *Vs0 = reinterpret_cast<__nv_bfloat16 *>(smem + L.v_off);
+    const int k_stage = gl * kPfKeys * (D + 8), v_stage = gl * kPfKeys * (DV + 8);   // elements per stage
     float *Ps = reinterpret_cast<float *>(smem + L.p_off);
     float *talk_s = reinterpret_cast<float *>(smem + L.talk_off);
     float *bias_s = reinterpret_cast<float *>(smem + L.bias_off);
@@ -131,26 +144,53 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
     const int ck = gl * D / 8, cv = gl * DV / 8;   // 16-byte pieces per staged cache row (this CTA's kv heads)
     __syncthreads();
     const float slope = slope_s[hl], hb = bias_s[hl];
+    const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
     const uint32_t ps_base = smem_u32(Ps);
+    int j_begin = 0, j_end = p_last + 1;
+    if (splits > 1) {
+        const int tiles = (p_last + kPfKeys) / kPfKeys, per = (tiles + splits - 1) / splits;
+        j_begin = min(j_end, static_cast<int>(blockIdx.x) * per * kPfKeys);
+        j_end = min(j_end, j_begin + per * kPfKeys);
+    }
 
-    for (int j0 = 0; j0 <= p_last; j0 += kPfKeys) {
-        // 1. stage keys and values
+    // keys and values of one tile -> shared memory stage `st` (cp.async; rows past the sequence's end are zero-filled)
+    auto stage_tile = [&](int j0, int st) {
+        __nv_bfloat16 *Kd = Ks0 + st * k_stage, *Vd = Vs0 + st * v_stage;
         for (int i = threadIdx.x; i < kPfKeys * ck; i += nthreads) {
             const int jj = i / ck, e = i % ck, j = j0 + jj;
             const bool ok = j < total;
             const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
             const int g = (e * 8) / D, d = (e * 8) % D;
-            cp_async_16(smem_u32(Ks + (g * kPfKeys + jj) * (D + 8) + d), kc + (slot * G + c_lo) * D + e * 8, ok ? 16 : 0);
+            cp_async_16(smem_u32(Kd + (g * kPfKeys + jj) * (D + 8) + d), kc + (slot * G + c_lo) * D + e * 8, ok ? 16 : 0);
         }
         for (int i = threadIdx.x; i < kPfKeys * cv; i += nthreads) {
             const int jj = i / cv, e = i % cv, j = j0 + jj;
             const bool ok = j < total;
             const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
             const int g = (e * 8) / DV, d = (e * 8) % DV;
-            cp_async_16(smem_u32(Vs + (g * kPfKeys + jj) * (DV + 8) + d), vc + (slot * G + c_lo) * DV + e * 8, ok ? 16 : 0);
+            cp_async_16(smem_u32(Vd + (g * kPfKeys + jj) * (DV + 8) + d), vc + (slot * G + c_lo) * DV + e * 8, ok ? 16 : 0);
         }
         cp_async_commit();
-        cp_async_wait_all();
+    };
+    if (stages > 1 && j_begin < j_end) stage_tile(j_begin, 0);
+
+    int it = 0;
+    for (int j0 = j_begin; j0 < j_end; j0 += kPfKeys, ++it) {
+        // 1. this tile's keys and values (with two stages: the next tile's copies are issued first and fly during the math)
+        int st = 0;
+        if (stages > 1) {
+            st = it & 1;
+            if (j0 + kPfKeys < j_end) {
+                stage_tile(j0 + kPfKeys, st ^ 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                cp_async_wait_all();
+            }
+        } else {
+            stage_tile(j0, 0);
+            cp_async_wait_all();
+        }
+        const __nv_bfloat16 *Ks = Ks0 + st * k_stage, *Vs = Vs0 + st * v_stage;
         __syncthreads();
 
         // 2. scores and weights of this warp's head
@@ -177,13 +217,26 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int row = rq + (e >> 1) * 8, j = j0 + nt * 8 + 2 * t4 + (e & 1), p = p0 + row;
-                w[e] = (row < rows && j <= p) ? sigmoid_weight(sacc[nt][e], a.scale, a.softcap, slope, static_cast<float>(p - j), hb) : 0.f;
+                w[e] = (row < rows && j <= p)
+                           ? sigmoid_weight_fast(sacc[nt][e], a.scale, a.softcap, inv_cap, slope, static_cast<float>(p - j), hb) : 0.f;
             }
-            float *dst = Ps + (hl * kPfRows + rq) * kPfPStride + nt * 8 + 2 * t4;
+            float *dst = Ps + (h * kPfRows + rq) * kPfPStride + nt * 8 + 2 * t4;
             *reinterpret_cast<float2 *>(dst) = make_float2(w[0], w[1]);
             *reinterpret_cast<float2 *>(dst + 8 * kPfPStride) = make_float2(w[2], w[3]);
         }
         if (cs > 1) {
+            // the other CTAs' heads: copy their slices of the tile's weights into this CTA's buffer (16-byte loads through
+            // distributed shared memory, all in flight at once), between two cluster barriers
+            cluster_arrive_release();
+            cluster_wait_acquire();
+            const int row_f4 = kPfPStride / 4, per_head = rows * row_f4, per_cta = hpc * per_head;   // float4 of the rows in use
+            for (int i = threadIdx.x; i < (cs - 1) * per_cta; i += nthreads) {
+                const int rr = i / per_cta, src_rank = rr >= rank ? rr + 1 : rr;
+                const int k = i % per_cta, hd = src_rank * hpc + k / per_head;
+                const int off = (hd * kPfRows * row_f4 + k % per_head) * 16;
+                const float4 v = ld_cluster_f4(mapa_shared(ps_base + off, static_cast<uint32_t>(src_rank)));
+                *reinterpret_cast<float4 *>(reinterpret_cast<unsigned char *>(Ps) + off) = v;
+            }
             cluster_arrive_release();
             cluster_wait_acquire();
         } else {
@@ -196,31 +249,39 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
             float m[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) m[i] = 0.f;
-            for (int g = 0; g < H; ++g) {
-                const float tg = talk_s[hl * H + g];
-                const int off = ((g % hpc) * kPfRows + rq) * kPfPStride + kk * 16 + 2 * t4;
-                float2 x0, x1, x2, x3;
-                if (cs > 1) {
-                    const uint32_t src = mapa_shared(ps_base + off * 4, static_cast<uint32_t>(g / hpc));
-                    x0 = ld_cluster_f2(src);
-                    x1 = ld_cluster_f2(src + 8 * kPfPStride * 4);
-                    x2 = ld_cluster_f2(src + 8 * 4);
-                    x3 = ld_cluster_f2(src + (8 * kPfPStride + 8) * 4);
-                } else {
-                    const float *src = Ps + off;
-                    x0 = *reinterpret_cast<const float2 *>(src);
-                    x1 = *reinterpret_cast<const float2 *>(src + 8 * kPfPStride);
-                    x2 = *reinterpret_cast<const float2 *>(src + 8);
-                    x3 = *reinterpret_cast<const float2 *>(src + 8 * kPfPStride + 8);
+            if (rows == 1) {
+                // one query row: lane = key of the tile; the A fragment's row 0 is gathered with shuffles
+                float mk = 0.f;
+                for (int g = 0; g < H; ++g) mk = fmaf(talk_s[hl * H + g], Ps[g * kPfRows * kPfPStride + lane], mk);
+                const int k0 = kk * 16 + 2 * t4;
+                const float v0 = __shfl_sync(0xffffffffu, mk, k0), v1 = __shfl_sync(0xffffffffu, mk, k0 + 1);
+                const float v4 = __shfl_sync(0xffffffffu, mk, k0 + 8), v5 = __shfl_sync(0xffffffffu, mk, k0 + 9);
+                if (rq == 0) {
+                    m[0] = v0;
+                    m[1] = v1;
+                    m[4] = v4;
+                    m[5] = v5;
                 }
-                m[0] = fmaf(tg, x0.x, m[0]);
-                m[1] = fmaf(tg, x0.y, m[1]);
-                m[2] = fmaf(tg, x1.x, m[2]);
-                m[3] = fmaf(tg, x1.y, m[3]);
-                m[4] = fmaf(tg, x2.x, m[4]);
-                m[5] = fmaf(tg, x2.y, m[5]);
-                m[6] = fmaf(tg, x3.x, m[6]);
-                m[7] = fmaf(tg, x3.y, m[7]);
+            } else {
+                const bool lower = rows > 8;     // rows 8 .. 15 exist
+                for (int g = 0; g < H; ++g) {
+                    const float tg = talk_s[hl * H + g];
+                    const float *src = Ps + (g * kPfRows + rq) * kPfPStride + kk * 16 + 2 * t4;
+                    const float2 x0 = *reinterpret_cast<const float2 *>(src);
+                    const float2 x2 = *reinterpret_cast<const float2 *>(src + 8);
+                    m[0] = fmaf(tg, x0.x, m[0]);
+                    m[1] = fmaf(tg, x0.y, m[1]);
+                    m[4] = fmaf(tg, x2.x, m[4]);
+                    m[5] = fmaf(tg, x2.y, m[5]);
+                    if (lower) {
+                        const float2 x1 = *reinterpret_cast<const float2 *>(src + 8 * kPfPStride);
+                        const float2 x3 = *reinterpret_cast<const float2 *>(src + 8 * kPfPStride + 8);
+                        m[2] = fmaf(tg, x1.x, m[2]);
+                        m[3] = fmaf(tg, x1.y, m[3]);
+                        m[6] = fmaf(tg, x3.x, m[6]);
+                        m[7] = fmaf(tg, x3.y, m[7]);
+                    }
+                }
             }
             uint32_t af[4];
             af[0] = pack2<__nv_bfloat16>(m[0], m[1]);
@@ -239,14 +300,18 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
                 }
             }
         }
-        if (cs > 1) {            // the other CTAs have read this tile's weights before the next tile overwrites them
-            cluster_arrive_release();
-            cluster_wait_acquire();
-        } else {
-            __syncthreads();
-        }
+        __syncthreads();   // this tile's keys, values and weights are done with (remote readers finished before the mix)
     }
 
+    if (partial) {   // this key split's float32 sums (one query row per sequence)
+        if (rq == 0) {
+            float *po = partial + (static_cast<int64_t>(tok0) * splits + blockIdx.x) * H * DV + h * DV;
+#pragma unroll
+            for (int nt = 0; nt < KMAX / 8; ++nt)
+                if (nt * 8 < DV) *reinterpret_cast<float2 *>(po + nt * 8 + 2 * t4) = make_float2(o[nt][0], o[nt][1]);
+        }
+        return;
+    }
     __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(a.out) + static_cast<int64_t>(tok0) * H * DV + h * DV;
 #pragma unroll
     for (int nt = 0; nt < KMAX / 8; ++nt) {
@@ -260,7 +325,8 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
 }
 
 template <int KMAX, int MAXWARPS>
-cudaError_t launch_prefill(const atoma_sigmoid_attn_args &a, int hpc, int gl, int cs, size_t smem_bytes, cudaStream_t stream) {
+cudaError_t launch_prefill(const atoma_sigmoid_attn_args &a, int hpc, int gl, int cs, int splits, float *partial, int stages,
+                           size_t smem_bytes, cudaStream_t stream) {
     static int attr_dev = -1;
     const int dev = current_device_info().ordinal;
     if (attr_dev != dev) {
@@ -268,7 +334,8 @@ cudaError_t launch_prefill(const atoma_sigmoid_attn_args &a, int hpc, int gl, in
         attr_dev = dev;
     }
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(static_cast<unsigned>((a.max_query_len + kPfRows - 1) / kPfRows), static_cast<unsigned>(a.B), static_cast<unsigned>(cs));
+    cfg.gridDim = dim3(static_cast<unsigned>(splits > 1 ? splits : (a.max_query_len + kPfRows - 1) / kPfRows), static_cast<unsigned>(a.B),
+                       static_cast<unsigned>(cs));
     cfg.blockDim = dim3(static_cast<unsigned>(32 * hpc));
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
@@ -288,17 +355,20 @@ cudaError_t launch_prefill(const atoma_sigmoid_attn_args &a, int hpc, int gl, in
     }
     cfg.attrs = attr;
     cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, sigmoid_attn_prefill_kernel<KMAX, MAXWARPS>, a, hpc, gl, cs);
+    return cudaLaunchKernelEx(&cfg, sigmoid_attn_prefill_kernel<KMAX, MAXWARPS>, a, hpc, gl, cs, splits, partial, stages);
 }
 
 }  // namespace
 
-// Takes the batch when it holds a portion longer than one token, in bfloat16, with head sizes the tiles cover.
+bool hyb_attn_split_reduce(const float *partial, void *out, int64_t T, int splits, int64_t n, uint32_t dtype, cudaStream_t stream);
+
+// Takes bfloat16 batches with head sizes the tiles cover: mixed batches and prompt portions by query tile, decode-only
+// batches by key split.
 bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, bool *taken) {
     *taken = false;
     const int64_t kmax = std::max(a.dim, a.vdim);
     auto al = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-    if (a.dtype != ATOMA_DTYPE_BF16 || a.max_query_len <= 1 || !a.query_start || a.dim % 16 || a.vdim % 16 || kmax > 128 ||
+    if (a.dtype != ATOMA_DTYPE_BF16 || a.max_query_len < 1 || !a.query_start || a.dim % 16 || a.vdim % 16 || kmax > 128 ||
         !al(a.q) || !al(a.k_cache) || !al(a.v_cache) || !al(a.out) || current_device_info().cc_major < 9)
         return true;
     // heads per CTA: the largest divisor of H that the register budget allows, with at most 8 CTAs per cluster and whole
@@ -310,23 +380,43 @@ bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, b
         if (H % cand || H / cand > 8) continue;
         if (cand % rep != 0 && rep % cand != 0) continue;
         const int g = cand % rep == 0 ? cand / rep : 1;
-        if (pf_layout(cand, g, H, static_cast<int>(a.dim), static_cast<int>(a.vdim)).total > 200 * 1024) continue;
+        if (pf_layout(cand, g, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 1).total > 200 * 1024) continue;
         hpc = cand;
         gl = g;
         break;
     }
     if (!hpc) return true;
     const int cs = H / hpc;
-    const PfLayout L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim));
+    // two staging buffers (the next tile's copies fly during the math) unless one buffer lets more CTAs share an SM
+    const int smem1 = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 1).total + 1024;
+    const int smem2 = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 2).total + 1024;
+    const int per_sm = 227 * 1024;
+    const int stages = (smem2 <= 200 * 1024 && per_sm / smem2 >= std::min(per_sm / smem1, 4)) ? 2 : 1;
+    const PfLayout L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), stages);
     *taken = true;
-    const cudaError_t e = kmax <= 64 ? launch_prefill<64, 16>(a, hpc, gl, cs, L.total, stream)
-                                     : launch_prefill<128, 8>(a, hpc, gl, cs, L.total, stream);
+    // decode-only batches: every sequence has ONE query row, so the keys are split over CTAs until the device is full;
+    // the splits' float32 sums are added in split order by a second kernel (no softmax: partial results simply add)
+    int splits = 1;
+    float *partial = nullptr;
+    if (a.max_query_len == 1 && a.max_seq_len > 2 * kPfKeys) {
+        const int64_t ctas = a.B * cs, tiles = (a.max_seq_len + kPfKeys - 1) / kPfKeys;
+        const int64_t want = (4 * current_device_info().sm_count + ctas - 1) / ctas;
+        splits = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({want, tiles / 2, 64})));
+        if (splits > 1) {
+            partial = static_cast<float *>(get_workspace(stream, static_cast<size_t>(a.T) * splits * a.H * a.vdim * 4, kWorkspaceHybridAttn));
+            if (!partial) return false;
+        }
+    }
+    const cudaError_t e = kmax <= 64 ? launch_prefill<64, 16>(a, hpc, gl, cs, splits, partial, stages, L.total, stream)
+                                     : launch_prefill<128, 8>(a, hpc, gl, cs, splits, partial, stages, L.total, stream);
     note_launch();
     if (e != cudaSuccess) {
         set_status(static_cast<int>(e), "sigmoid_attn_prefill_kernel: %s", cudaGetErrorString(e));
         return false;
     }
-    return check_launch("sigmoid_attn_prefill_kernel");
+    if (!check_launch("sigmoid_attn_prefill_kernel")) return false;
+    if (splits > 1) return hyb_attn_split_reduce(partial, a.out, a.T, splits, a.H * a.vdim, a.dtype, stream);
+    return true;
 }
 
 }  // namespace atoma

@@ -19,6 +19,7 @@
 namespace atoma {
 
 int g_hybrid_debug = 0;
+bool hyb_attn_split_reduce(const float *partial, void *out, int64_t T, int splits, int64_t n, uint32_t dtype, cudaStream_t stream);
 
 namespace {
 
@@ -325,6 +326,7 @@ __global__ void __launch_bounds__(32 * kScanSeg) mingru_scan_kernel(const T *__r
     const float bz = (live && bias) ? bias[c] : 0.f, bx = (live && bias) ? bias[S + c] : 0.f, bg = (live && bias) ? bias[2 * S + c] : 0.f;
     float A = 1.f, B = 0.f;
     if (live)
+#pragma unroll 8
         for (int t = lo; t < hi; ++t) {
             const T *r = zxg + static_cast<int64_t>(t) * 3 * S;
             float z, cand;
@@ -339,6 +341,7 @@ __global__ void __launch_bounds__(32 * kScanSeg) mingru_scan_kernel(const T *__r
     float s = (live && context_lens[b] > 0) ? *st : 0.f;
     for (int k = 0; k < seg; ++k) s = sa[k][lane] * s + sb[k][lane];
     if (!live) return;
+#pragma unroll 8
     for (int t = lo; t < hi; ++t) {
         const T *r = zxg + static_cast<int64_t>(t) * 3 * S;
         float z, cand;
@@ -572,9 +575,13 @@ bool hyb_attention_general(const atoma_sigmoid_attn_args &a, cudaStream_t stream
     if (!finish(HYB_DISPATCH(a.dtype, CALL), "sigmoid_attn_general_kernel")) return false;
 #undef CALL
     if (splits == 1) return true;
-#define CALL(TT) launch_ex(attn_split_reduce_kernel<TT>, dim3(static_cast<unsigned>(a.T)), dim3(256), 0, stream, partial, \
-                           static_cast<TT *>(a.out), splits, static_cast<int>(a.H * a.vdim))
-    return finish(HYB_DISPATCH(a.dtype, CALL), "attn_split_reduce_kernel");
+    return hyb_attn_split_reduce(partial, a.out, a.T, splits, a.H * a.vdim, a.dtype, stream);
+}
+
+bool hyb_attn_split_reduce(const float *partial, void *out, int64_t T, int splits, int64_t n, uint32_t dtype, cudaStream_t stream) {
+#define CALL(TT) launch_ex(attn_split_reduce_kernel<TT>, dim3(static_cast<unsigned>(T)), dim3(256), 0, stream, partial, \
+                           static_cast<TT *>(out), splits, static_cast<int>(n))
+    return finish(HYB_DISPATCH(dtype, CALL), "attn_split_reduce_kernel");
 #undef CALL
 }
 

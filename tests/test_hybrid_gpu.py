@@ -160,6 +160,28 @@ def test_sigmoid_attention_on_a_mixed_batch(dtype, general, H, G, D, Dv):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("general", [False, True])
+@pytest.mark.parametrize("H,G,D,Dv", [(4, 2, 16, 24), (8, 4, 96, 96), (32, 8, 64, 64), (16, 2, 128, 128), (3, 3, 20, 12)])
+def test_sigmoid_attention_on_a_decode_only_batch(dtype, general, H, G, D, Dv):
+    """One query token per sequence, contexts from nothing to a thousand keys: the keys are split over CTAs and the splits'
+    sums added."""
+    g = torch.Generator().manual_seed(8)
+    bs = 16
+    seqs = [(300, 1), (0, 1), (65, 1), (1000, 1), (31, 1), (32, 1)]
+    q, kc, vc, pos, tseq, bt, ref = _paged_batch(g, seqs, H, G, D, Dv, bs, dtype)
+    slopes = torch.tensor(lo.distance_slopes(H))
+    pb = torch.randn(H, generator=g) - 2.0
+    talk = torch.eye(H) + 0.3 * torch.randn(H, H, generator=g)
+    m = {"heads": H, "kv_heads": G, "scale": 0.2, "softcap": 8.0}
+    _ops().debug_flags(2 if general else 0)
+    out = _ops().sigmoid_attention_paged(q, kc, vc, pos, tseq, bt, slopes.to(DEV), pb.to(DEV), talk.to(DEV), H, G, D, Dv, bs,
+                                         0.2, 8.0, 1)
+    for b, (qq, kk, vv, c) in enumerate(ref):
+        want = lo.attention_core(qq, kk, vv, m, pb.double(), talk.double(), first_position=c).reshape(1, H * Dv)
+        assert nerr(out[b:b + 1], want) < (1e-5 if dtype == torch.float32 else 1e-2), (b, c)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("general", [False, True])
 def test_a_single_far_key_is_found_wherever_it_lies(dtype, general):
     """Head biases push every ordinary weight to ~0; one key is made to stand out by a q . k large enough to beat the distance
     bias from hundreds of positions away (the query looks along one dimension that every other key has at zero).  Its value
