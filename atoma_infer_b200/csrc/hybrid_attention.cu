@@ -33,14 +33,15 @@ namespace {
 
 using namespace hybrid;
 
-constexpr int kPfRows = 16, kPfKeys = 32, kPfPStride = kPfKeys + 4;   // +4: a two-way bank conflict at most, and two CTAs fit an SM at 32 heads
+constexpr int kPfRows = 16, kPfKeys = 32, kPfPStride = kPfKeys + 8;
 
 struct PfLayout {
     int k_off, v_off, p_off, talk_off, bias_off, slope_off, total;
 };
 
 // hpc = heads per CTA, gl = kv heads a CTA stages, H = all heads (the talking-heads matrix rows are kept whole)
-__host__ __device__ inline PfLayout pf_layout(int hpc, int gl, int H, int D, int DV, int stages) {
+// prow = query rows the weight buffer holds (16; 1 for decode-only batches, which lets several CTAs share an SM)
+__host__ __device__ inline PfLayout pf_layout(int hpc, int gl, int H, int D, int DV, int stages, int prow) {
     PfLayout l;
     int off = 0;
     l.k_off = off;
@@ -48,7 +49,7 @@ __host__ __device__ inline PfLayout pf_layout(int hpc, int gl, int H, int D, int
     l.v_off = off;
     off += stages * gl * kPfKeys * (DV + 8) * 2;
     l.p_off = off;
-    off += H * kPfRows * kPfPStride * 4;   // every head's weights of the tile: own heads computed here, the rest copied in
+    off += H * prow * kPfPStride * 4;   // every head's weights of the tile: own heads computed here, the rest copied in
     l.talk_off = off;
     off += hpc * H * 4;
     l.bias_off = off;
@@ -99,7 +100,8 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
     const int c_lo = (rank * hpc) / (H / G);             // first kv head this CTA stages
     const int c = h / (H / G) - c_lo;                    // this warp's kv head among the staged ones
     const int nthreads = blockDim.x;
-    const PfLayout L = pf_layout(hpc, gl, H, D, DV, stages);
+    const int prow = splits > 1 ? 1 : kPfRows;
+    const PfLayout L = pf_layout(hpc, gl, H, D, DV, stages, prow);
     __nv_bfloat16 *Ks0 = reinterpret_cast<__nv_bfloat16 *>(smem + L.k_off);
     __nv_bfloat16 *Vs0 = reinterpret_cast<__nv_bfloat16 *>(smem + L.v_off);
     const int k_stage = gl * kPfKeys * (D + 8), v_stage = gl * kPfKeys * (DV + 8);   // elements per stage
@@ -156,19 +158,26 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
     // keys and values of one tile -> shared memory stage `st` (cp.async; rows past the sequence's end are zero-filled)
     auto stage_tile = [&](int j0, int st) {
         __nv_bfloat16 *Kd = Ks0 + st * k_stage, *Vd = Vs0 + st * v_stage;
-        for (int i = threadIdx.x; i < kPfKeys * ck; i += nthreads) {
-            const int jj = i / ck, e = i % ck, j = j0 + jj;
-            const bool ok = j < total;
-            const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
+        // warp w takes keys w, w + warps, ...; lane l the 16-byte pieces l, l + 32, ... of a row (their kv head and offset
+        // do not depend on the key, so the divisions are hoisted out of the key loop)
+        const int wid = threadIdx.x >> 5, nw = nthreads >> 5;
+        for (int e = lane; e < ck; e += 32) {
             const int g = (e * 8) / D, d = (e * 8) % D;
-            cp_async_16(smem_u32(Kd + (g * kPfKeys + jj) * (D + 8) + d), kc + (slot * G + c_lo) * D + e * 8, ok ? 16 : 0);
+            for (int jj = wid; jj < kPfKeys; jj += nw) {
+                const int j = j0 + jj;
+                const bool ok = j < total;
+                const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
+                cp_async_16(smem_u32(Kd + (g * kPfKeys + jj) * (D + 8) + d), kc + (slot * G + c_lo) * D + e * 8, ok ? 16 : 0);
+            }
         }
-        for (int i = threadIdx.x; i < kPfKeys * cv; i += nthreads) {
-            const int jj = i / cv, e = i % cv, j = j0 + jj;
-            const bool ok = j < total;
-            const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
+        for (int e = lane; e < cv; e += 32) {
             const int g = (e * 8) / DV, d = (e * 8) % DV;
-            cp_async_16(smem_u32(Vd + (g * kPfKeys + jj) * (DV + 8) + d), vc + (slot * G + c_lo) * DV + e * 8, ok ? 16 : 0);
+            for (int jj = wid; jj < kPfKeys; jj += nw) {
+                const int j = j0 + jj;
+                const bool ok = j < total;
+                const int64_t slot = ok ? static_cast<int64_t>(bt[j / bs]) * bs + j % bs : 0;
+                cp_async_16(smem_u32(Vd + (g * kPfKeys + jj) * (DV + 8) + d), vc + (slot * G + c_lo) * DV + e * 8, ok ? 16 : 0);
+            }
         }
         cp_async_commit();
     };
@@ -220,22 +229,32 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
                 w[e] = (row < rows && j <= p)
                            ? sigmoid_weight_fast(sacc[nt][e], a.scale, a.softcap, inv_cap, slope, static_cast<float>(p - j), hb) : 0.f;
             }
-            float *dst = Ps + (h * kPfRows + rq) * kPfPStride + nt * 8 + 2 * t4;
-            *reinterpret_cast<float2 *>(dst) = make_float2(w[0], w[1]);
-            *reinterpret_cast<float2 *>(dst + 8 * kPfPStride) = make_float2(w[2], w[3]);
+            float *dst = Ps + (h * prow + rq) * kPfPStride + nt * 8 + 2 * t4;
+            if (rq < prow) *reinterpret_cast<float2 *>(dst) = make_float2(w[0], w[1]);
+            if (rq + 8 < prow) *reinterpret_cast<float2 *>(dst + 8 * kPfPStride) = make_float2(w[2], w[3]);
         }
         if (cs > 1) {
             // the other CTAs' heads: copy their slices of the tile's weights into this CTA's buffer (16-byte loads through
             // distributed shared memory, all in flight at once), between two cluster barriers
             cluster_arrive_release();
             cluster_wait_acquire();
-            const int row_f4 = kPfPStride / 4, per_head = rows * row_f4, per_cta = hpc * per_head;   // float4 of the rows in use
-            for (int i = threadIdx.x; i < (cs - 1) * per_cta; i += nthreads) {
-                const int rr = i / per_cta, src_rank = rr >= rank ? rr + 1 : rr;
-                const int k = i % per_cta, hd = src_rank * hpc + k / per_head;
-                const int off = (hd * kPfRows * row_f4 + k % per_head) * 16;
-                const float4 v = ld_cluster_f4(mapa_shared(ps_base + off, static_cast<uint32_t>(src_rank)));
-                *reinterpret_cast<float4 *>(reinterpret_cast<unsigned char *>(Ps) + off) = v;
+            const int row_f4 = kPfPStride / 4, per_head = rows * row_f4;   // float4 of a head's rows in use (contiguous)
+            for (int idx = threadIdx.x; idx < per_head; idx += nthreads)
+            for (int hd0 = 0; hd0 < H; hd0 += 4) {
+                float4 v[4];
+                int off[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int hd = hd0 + u, src_rank = hd / hpc;
+                    off[u] = -1;
+                    if (hd < H && src_rank != rank) {
+                        off[u] = (hd * prow * row_f4 + idx) * 16;
+                        v[u] = ld_cluster_f4(mapa_shared(ps_base + off[u], static_cast<uint32_t>(src_rank)));
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (off[u] >= 0) *reinterpret_cast<float4 *>(reinterpret_cast<unsigned char *>(Ps) + off[u]) = v[u];
             }
             cluster_arrive_release();
             cluster_wait_acquire();
@@ -244,15 +263,17 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
         }
 
         // 3. mix the heads' weights and apply them to this warp's values
+        float mk = 0.f;   // one query row: lane = key of the tile
+        if (rows == 1)
+#pragma unroll 4
+            for (int g = 0; g < H; ++g) mk = fmaf(talk_s[hl * H + g], Ps[g * prow * kPfPStride + lane], mk);
 #pragma unroll
         for (int kk = 0; kk < kPfKeys / 16; ++kk) {
             float m[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) m[i] = 0.f;
             if (rows == 1) {
-                // one query row: lane = key of the tile; the A fragment's row 0 is gathered with shuffles
-                float mk = 0.f;
-                for (int g = 0; g < H; ++g) mk = fmaf(talk_s[hl * H + g], Ps[g * kPfRows * kPfPStride + lane], mk);
+                // the A fragment's row 0 is gathered with shuffles
                 const int k0 = kk * 16 + 2 * t4;
                 const float v0 = __shfl_sync(0xffffffffu, mk, k0), v1 = __shfl_sync(0xffffffffu, mk, k0 + 1);
                 const float v4 = __shfl_sync(0xffffffffu, mk, k0 + 8), v5 = __shfl_sync(0xffffffffu, mk, k0 + 9);
@@ -264,9 +285,10 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
                 }
             } else {
                 const bool lower = rows > 8;     // rows 8 .. 15 exist
+#pragma unroll 4
                 for (int g = 0; g < H; ++g) {
                     const float tg = talk_s[hl * H + g];
-                    const float *src = Ps + (g * kPfRows + rq) * kPfPStride + kk * 16 + 2 * t4;
+                    const float *src = Ps + (g * prow + rq) * kPfPStride + kk * 16 + 2 * t4;
                     const float2 x0 = *reinterpret_cast<const float2 *>(src);
                     const float2 x2 = *reinterpret_cast<const float2 *>(src + 8);
                     m[0] = fmaf(tg, x0.x, m[0]);
@@ -380,19 +402,13 @@ bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, b
         if (H % cand || H / cand > 8) continue;
         if (cand % rep != 0 && rep % cand != 0) continue;
         const int g = cand % rep == 0 ? cand / rep : 1;
-        if (pf_layout(cand, g, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 1).total > 200 * 1024) continue;
+        if (pf_layout(cand, g, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 1, kPfRows).total > 200 * 1024) continue;
         hpc = cand;
         gl = g;
         break;
     }
     if (!hpc) return true;
     const int cs = H / hpc;
-    // two staging buffers (the next tile's copies fly during the math) unless one buffer lets more CTAs share an SM
-    const int smem1 = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 1).total + 1024;
-    const int smem2 = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 2).total + 1024;
-    const int per_sm = 227 * 1024;
-    const int stages = (smem2 <= 200 * 1024 && per_sm / smem2 >= std::min(per_sm / smem1, 4)) ? 2 : 1;
-    const PfLayout L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), stages);
     *taken = true;
     // decode-only batches: every sequence has ONE query row, so the keys are split over CTAs until the device is full;
     // the splits' float32 sums are added in split order by a second kernel (no softmax: partial results simply add)
@@ -400,13 +416,18 @@ bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, b
     float *partial = nullptr;
     if (a.max_query_len == 1 && a.max_seq_len > 2 * kPfKeys) {
         const int64_t ctas = a.B * cs, tiles = (a.max_seq_len + kPfKeys - 1) / kPfKeys;
-        const int64_t want = (4 * current_device_info().sm_count + ctas - 1) / ctas;
+        const int64_t want = (6 * current_device_info().sm_count + ctas - 1) / ctas;
         splits = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({want, tiles / 2, 64})));
         if (splits > 1) {
             partial = static_cast<float *>(get_workspace(stream, static_cast<size_t>(a.T) * splits * a.H * a.vdim * 4, kWorkspaceHybridAttn));
             if (!partial) return false;
         }
     }
+    // two staging buffers (the next tile's copies fly during the math) whenever they fit
+    // (measured at 32 heads of 128: one double-buffered CTA per SM beats two single-buffered ones, 8.1 vs 9.1 ms at 4k tokens)
+    const int prow = splits > 1 ? 1 : kPfRows;
+    const int stages = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 2, prow).total <= 200 * 1024 ? 2 : 1;
+    const PfLayout L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), stages, prow);
     const cudaError_t e = kmax <= 64 ? launch_prefill<64, 16>(a, hpc, gl, cs, splits, partial, stages, L.total, stream)
                                      : launch_prefill<128, 8>(a, hpc, gl, cs, splits, partial, stages, L.total, stream);
     note_launch();
