@@ -33,7 +33,10 @@ namespace {
 
 using namespace hybrid;
 
-constexpr int kPfRows = 16, kPfKeys = 32, kPfPStride = kPfKeys + 8;
+constexpr int kPfRows = 16;
+// keys per tile: 32 for portions (the weight buffer holds 16 rows of every head), 64 for decode-only batches (one row:
+// half as many barrier rounds per key)
+constexpr int kPfKeysPrompt = 32, kPfKeysDecode = 64;
 
 struct PfLayout {
     int k_off, v_off, p_off, talk_off, bias_off, slope_off, total;
@@ -41,7 +44,8 @@ struct PfLayout {
 
 // hpc = heads per CTA, gl = kv heads a CTA stages, H = all heads (the talking-heads matrix rows are kept whole)
 // prow = query rows the weight buffer holds (16; 1 for decode-only batches, which lets several CTAs share an SM)
-__host__ __device__ inline PfLayout pf_layout(int hpc, int gl, int H, int D, int DV, int stages, int prow) {
+__host__ __device__ inline PfLayout pf_layout(int hpc, int gl, int H, int D, int DV, int stages, int prow, int kPfKeys) {
+    const int kPfPStride = kPfKeys + 8;
     PfLayout l;
     int off = 0;
     l.k_off = off;
@@ -76,9 +80,10 @@ __device__ __forceinline__ float sigmoid_weight_fast(float dot, float scale, flo
     return __fdividef(1.f, 1.f + __expf(-s));
 }
 
-template <int KMAX, int MAXWARPS>
+template <int KMAX, int MAXWARPS, int kPfKeys>
 __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(const atoma_sigmoid_attn_args a, int hpc, int gl, int cs, int splits,
                                                                              float *__restrict__ partial, int stages) {
+    constexpr int kPfPStride = kPfKeys + 8;
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -101,7 +106,7 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
     const int c = h / (H / G) - c_lo;                    // this warp's kv head among the staged ones
     const int nthreads = blockDim.x;
     const int prow = splits > 1 ? 1 : kPfRows;
-    const PfLayout L = pf_layout(hpc, gl, H, D, DV, stages, prow);
+    const PfLayout L = pf_layout(hpc, gl, H, D, DV, stages, prow, kPfKeys);
     __nv_bfloat16 *Ks0 = reinterpret_cast<__nv_bfloat16 *>(smem + L.k_off);
     __nv_bfloat16 *Vs0 = reinterpret_cast<__nv_bfloat16 *>(smem + L.v_off);
     const int k_stage = gl * kPfKeys * (D + 8), v_stage = gl * kPfKeys * (DV + 8);   // elements per stage
@@ -263,10 +268,16 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
         }
 
         // 3. mix the heads' weights and apply them to this warp's values
-        float mk = 0.f;   // one query row: lane = key of the tile
+        float mk[kPfKeys / 32];   // one query row: lane = keys lane, lane + 32, ... of the tile
+#pragma unroll
+        for (int u = 0; u < kPfKeys / 32; ++u) mk[u] = 0.f;
         if (rows == 1)
 #pragma unroll 4
-            for (int g = 0; g < H; ++g) mk = fmaf(talk_s[hl * H + g], Ps[g * prow * kPfPStride + lane], mk);
+            for (int g = 0; g < H; ++g) {
+                const float tg = talk_s[hl * H + g];
+#pragma unroll
+                for (int u = 0; u < kPfKeys / 32; ++u) mk[u] = fmaf(tg, Ps[g * prow * kPfPStride + u * 32 + lane], mk[u]);
+            }
 #pragma unroll
         for (int kk = 0; kk < kPfKeys / 16; ++kk) {
             float m[8];
@@ -274,9 +285,10 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
             for (int i = 0; i < 8; ++i) m[i] = 0.f;
             if (rows == 1) {
                 // the A fragment's row 0 is gathered with shuffles
-                const int k0 = kk * 16 + 2 * t4;
-                const float v0 = __shfl_sync(0xffffffffu, mk, k0), v1 = __shfl_sync(0xffffffffu, mk, k0 + 1);
-                const float v4 = __shfl_sync(0xffffffffu, mk, k0 + 8), v5 = __shfl_sync(0xffffffffu, mk, k0 + 9);
+                const int k0 = (kk * 16) % 32 + 2 * t4;
+                const float mv = mk[(kk * 16) / 32];
+                const float v0 = __shfl_sync(0xffffffffu, mv, k0), v1 = __shfl_sync(0xffffffffu, mv, k0 + 1);
+                const float v4 = __shfl_sync(0xffffffffu, mv, k0 + 8), v5 = __shfl_sync(0xffffffffu, mv, k0 + 9);
                 if (rq == 0) {
                     m[0] = v0;
                     m[1] = v1;
@@ -346,13 +358,13 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
     }
 }
 
-template <int KMAX, int MAXWARPS>
+template <int KMAX, int MAXWARPS, int KEYS>
 cudaError_t launch_prefill(const atoma_sigmoid_attn_args &a, int hpc, int gl, int cs, int splits, float *partial, int stages,
                            size_t smem_bytes, cudaStream_t stream) {
     static int attr_dev = -1;
     const int dev = current_device_info().ordinal;
     if (attr_dev != dev) {
-        cudaFuncSetAttribute(sigmoid_attn_prefill_kernel<KMAX, MAXWARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(sigmoid_attn_prefill_kernel<KMAX, MAXWARPS, KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr_dev = dev;
     }
     cudaLaunchConfig_t cfg{};
@@ -377,7 +389,7 @@ cudaError_t launch_prefill(const atoma_sigmoid_attn_args &a, int hpc, int gl, in
     }
     cfg.attrs = attr;
     cfg.numAttrs = n;
-    return cudaLaunchKernelEx(&cfg, sigmoid_attn_prefill_kernel<KMAX, MAXWARPS>, a, hpc, gl, cs, splits, partial, stages);
+    return cudaLaunchKernelEx(&cfg, sigmoid_attn_prefill_kernel<KMAX, MAXWARPS, KEYS>, a, hpc, gl, cs, splits, partial, stages);
 }
 
 }  // namespace
@@ -402,7 +414,7 @@ bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, b
         if (H % cand || H / cand > 8) continue;
         if (cand % rep != 0 && rep % cand != 0) continue;
         const int g = cand % rep == 0 ? cand / rep : 1;
-        if (pf_layout(cand, g, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 1, kPfRows).total > 200 * 1024) continue;
+        if (pf_layout(cand, g, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 1, kPfRows, kPfKeysPrompt).total > 200 * 1024) continue;
         hpc = cand;
         gl = g;
         break;
@@ -414,8 +426,8 @@ bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, b
     // the splits' float32 sums are added in split order by a second kernel (no softmax: partial results simply add)
     int splits = 1;
     float *partial = nullptr;
-    if (a.max_query_len == 1 && a.max_seq_len > 2 * kPfKeys) {
-        const int64_t ctas = a.B * cs, tiles = (a.max_seq_len + kPfKeys - 1) / kPfKeys;
+    if (a.max_query_len == 1 && a.max_seq_len > 2 * kPfKeysDecode) {
+        const int64_t ctas = a.B * cs, tiles = (a.max_seq_len + kPfKeysDecode - 1) / kPfKeysDecode;
         const int64_t want = (6 * current_device_info().sm_count + ctas - 1) / ctas;
         splits = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({want, tiles / 2, 64})));
         if (splits > 1) {
@@ -425,11 +437,22 @@ bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, b
     }
     // two staging buffers (the next tile's copies fly during the math) whenever they fit
     // (measured at 32 heads of 128: one double-buffered CTA per SM beats two single-buffered ones, 8.1 vs 9.1 ms at 4k tokens)
-    const int prow = splits > 1 ? 1 : kPfRows;
-    const int stages = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 2, prow).total <= 200 * 1024 ? 2 : 1;
-    const PfLayout L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), stages, prow);
-    const cudaError_t e = kmax <= 64 ? launch_prefill<64, 16>(a, hpc, gl, cs, splits, partial, stages, L.total, stream)
-                                     : launch_prefill<128, 8>(a, hpc, gl, cs, splits, partial, stages, L.total, stream);
+    const int prow = splits > 1 ? 1 : kPfRows, keys = splits > 1 ? kPfKeysDecode : kPfKeysPrompt;
+    int stages = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 2, prow, keys).total <= 200 * 1024 ? 2 : 1;
+    PfLayout L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), stages, prow, keys);
+    if (L.total > 200 * 1024) {   // many kv heads per CTA at 64 keys: the decode-only batch runs as one-row tiles of 32 keys, unsplit
+        splits = 1;
+        partial = nullptr;
+        stages = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 2, kPfRows, kPfKeysPrompt).total <= 200 * 1024 ? 2 : 1;
+        L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), stages, kPfRows, kPfKeysPrompt);
+    }
+    cudaError_t e;
+    if (splits > 1)
+        e = kmax <= 64 ? launch_prefill<64, 16, kPfKeysDecode>(a, hpc, gl, cs, splits, partial, stages, L.total, stream)
+                       : launch_prefill<128, 8, kPfKeysDecode>(a, hpc, gl, cs, splits, partial, stages, L.total, stream);
+    else
+        e = kmax <= 64 ? launch_prefill<64, 16, kPfKeysPrompt>(a, hpc, gl, cs, splits, partial, stages, L.total, stream)
+                       : launch_prefill<128, 8, kPfKeysPrompt>(a, hpc, gl, cs, splits, partial, stages, L.total, stream);
     note_launch();
     if (e != cudaSuccess) {
         set_status(static_cast<int>(e), "sigmoid_attn_prefill_kernel: %s", cudaGetErrorString(e));
