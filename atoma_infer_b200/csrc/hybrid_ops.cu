@@ -168,7 +168,7 @@ __device__ __forceinline__ float dot_row_vec(const float *__restrict__ q, const 
 }
 constexpr int kGenThreads = 256;
 constexpr int kGenKeys = 32;      // keys per pass
-constexpr int kGenMaxOut = 16;    // outputs per thread: H * vdim <= 4096
+constexpr int kGenMaxOut = 32;    // outputs per thread: H * vdim <= 8192
 
 template <typename T>
 __global__ void __launch_bounds__(kGenThreads) sigmoid_attn_general_kernel(const atoma_sigmoid_attn_args a, int splits,
@@ -325,14 +325,25 @@ __global__ void __launch_bounds__(32 * kScanSeg) mingru_scan_kernel(const T *__r
     const int lo = t0 + min(n, seg * per), hi = t0 + min(n, (seg + 1) * per);
     const float bz = (live && bias) ? bias[c] : 0.f, bx = (live && bias) ? bias[S + c] : 0.f, bg = (live && bias) ? bias[2 * S + c] : 0.f;
     float A = 1.f, B = 0.f;
+    constexpr int kBatch = 8;   // tokens whose loads are issued together before any of them is used
     if (live)
-#pragma unroll 8
-        for (int t = lo; t < hi; ++t) {
-            const T *r = zxg + static_cast<int64_t>(t) * 3 * S;
-            float z, cand;
-            mingru_gates(to_f(r[c]) + bz, to_f(r[S + c]) + bx, z, cand);
-            A = (1.f - z) * A;
-            B = (1.f - z) * B + z * cand;
+        for (int t = lo; t < hi; t += kBatch) {
+            T zr[kBatch], ur[kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i)
+                if (t + i < hi) {
+                    const T *r = zxg + static_cast<int64_t>(t + i) * 3 * S;
+                    zr[i] = r[c];
+                    ur[i] = r[S + c];
+                }
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i)
+                if (t + i < hi) {
+                    float z, cand;
+                    mingru_gates(to_f(zr[i]) + bz, to_f(ur[i]) + bx, z, cand);
+                    A = (1.f - z) * A;
+                    B = (1.f - z) * B + z * cand;
+                }
         }
     sa[seg][lane] = A;
     sb[seg][lane] = B;
@@ -341,13 +352,24 @@ __global__ void __launch_bounds__(32 * kScanSeg) mingru_scan_kernel(const T *__r
     float s = (live && context_lens[b] > 0) ? *st : 0.f;
     for (int k = 0; k < seg; ++k) s = sa[k][lane] * s + sb[k][lane];
     if (!live) return;
-#pragma unroll 8
-    for (int t = lo; t < hi; ++t) {
-        const T *r = zxg + static_cast<int64_t>(t) * 3 * S;
-        float z, cand;
-        mingru_gates(to_f(r[c]) + bz, to_f(r[S + c]) + bx, z, cand);
-        s = (1.f - z) * s + z * cand;
-        out[static_cast<int64_t>(t) * S + c] = from_f<T>(s * silu(to_f(r[2 * S + c]) + bg));
+    for (int t = lo; t < hi; t += kBatch) {
+        T zr[kBatch], ur[kBatch], gr[kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i)
+            if (t + i < hi) {
+                const T *r = zxg + static_cast<int64_t>(t + i) * 3 * S;
+                zr[i] = r[c];
+                ur[i] = r[S + c];
+                gr[i] = r[2 * S + c];
+            }
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i)
+            if (t + i < hi) {
+                float z, cand;
+                mingru_gates(to_f(zr[i]) + bz, to_f(ur[i]) + bx, z, cand);
+                s = (1.f - z) * s + z * cand;
+                out[static_cast<int64_t>(t + i) * S + c] = from_f<T>(s * silu(to_f(gr[i]) + bg));
+            }
     }
     if (seg == kScanSeg - 1) *st = s;
 }

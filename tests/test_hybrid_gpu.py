@@ -133,7 +133,7 @@ def _paged_batch(g, seqs, H, G, D, Dv, bs, dtype, scale_q=1.0, k_zero_dim=None):
 
 
 ATTN_SHAPES = [(4, 2, 16, 24), (4, 4, 32, 32), (6, 1, 8, 16), (2, 2, 64, 64), (8, 4, 96, 96), (3, 3, 20, 12),
-               (32, 8, 64, 64), (16, 2, 128, 128), (12, 4, 32, 48), (32, 32, 128, 96)]   # the last rows spread heads over a cluster
+               (32, 8, 64, 64), (16, 2, 128, 128), (12, 4, 32, 48), (32, 32, 128, 96), (36, 4, 16, 136)]   # the last rows spread heads over a cluster
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -414,3 +414,19 @@ def test_greedy_generation_through_the_scheduler(tmp_path):
                 break
             assert int(lg.argmax()) == tok
             t.append(tok)
+
+
+def test_command_line_generates_through_the_registry(tmp_path, capsys):
+    from atoma_infer_b200 import checkpoint
+    from atoma_infer_b200.__main__ import main
+    cfg, w, g = build("mixed", 5)
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    checkpoint.write_safetensors(tmp_path / "model.safetensors", {k: v.to(torch.bfloat16) for k, v in w.items()})
+    assert main(["generate", "--model", str(tmp_path), "--prompt-ids", "3,4,5,6", "--prompt-ids", "9", "--max-new-tokens", "3",
+                 "--dtype", "float32", "--max-tokens", "128", "--max-live", "2"]) == 0
+    lines = [json.loads(x) for x in capsys.readouterr().out.strip().splitlines() if x.startswith("{")]
+    assert [x["prompt"] for x in lines] == [[3, 4, 5, 6], [9]] and all(len(x["generated"]) == 3 for x in lines)
+    t = [3, 4, 5, 6]
+    lg = lo.forward(cfg, w, t)[-1]
+    if float(torch.topk(lg, 2).values[0] - torch.topk(lg, 2).values[1]) > 1e-3:
+        assert lines[0]["generated"][0] == int(lg.argmax())
