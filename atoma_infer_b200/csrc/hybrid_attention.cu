@@ -225,6 +225,23 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
                 }
             }
         }
+        if (prow == 1) {
+            // decode-only batch: the one query row's raw scores sit in lanes 0..3; spread them over the warp (lane = key) through
+            // the weight buffer so that every lane evaluates its own keys' weights instead of four lanes evaluating all of them
+            float *prow_s = Ps + h * kPfPStride;
+            if (rq == 0) {
+#pragma unroll
+                for (int nt = 0; nt < kPfKeys / 8; ++nt)
+                    *reinterpret_cast<float2 *>(prow_s + nt * 8 + 2 * t4) = make_float2(sacc[nt][0], sacc[nt][1]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int u = 0; u < kPfKeys / 32; ++u) {
+                const int j = j0 + u * 32 + lane;
+                const float raw = prow_s[u * 32 + lane];
+                prow_s[u * 32 + lane] = j <= p0 ? sigmoid_weight_fast(raw, a.scale, a.softcap, inv_cap, slope, static_cast<float>(p0 - j), hb) : 0.f;
+            }
+        } else {
 #pragma unroll
         for (int nt = 0; nt < kPfKeys / 8; ++nt) {
             float w[4];
@@ -235,8 +252,9 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
                            ? sigmoid_weight_fast(sacc[nt][e], a.scale, a.softcap, inv_cap, slope, static_cast<float>(p - j), hb) : 0.f;
             }
             float *dst = Ps + (h * prow + rq) * kPfPStride + nt * 8 + 2 * t4;
-            if (rq < prow) *reinterpret_cast<float2 *>(dst) = make_float2(w[0], w[1]);
-            if (rq + 8 < prow) *reinterpret_cast<float2 *>(dst + 8 * kPfPStride) = make_float2(w[2], w[3]);
+            *reinterpret_cast<float2 *>(dst) = make_float2(w[0], w[1]);
+            *reinterpret_cast<float2 *>(dst + 8 * kPfPStride) = make_float2(w[2], w[3]);
+        }
         }
         if (cs > 1) {
             // the other CTAs' heads: copy their slices of the tile's weights into this CTA's buffer (16-byte loads through
@@ -428,6 +446,7 @@ bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, b
     float *partial = nullptr;
     if (a.max_query_len == 1 && a.max_seq_len > 2 * kPfKeysDecode) {
         const int64_t ctas = a.B * cs, tiles = (a.max_seq_len + kPfKeysDecode - 1) / kPfKeysDecode;
+        // (measured: the time does not depend on this factor between 2 and 24 — the kernel is bound by its per-tile work)
         const int64_t want = (6 * current_device_info().sm_count + ctas - 1) / ctas;
         splits = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({want, tiles / 2, 64})));
         if (splits > 1) {
