@@ -44,8 +44,7 @@ struct PfLayout {
 
 // hpc = heads per CTA, gl = kv heads a CTA stages, H = all heads (the talking-heads matrix rows are kept whole)
 // prow = query rows the weight buffer holds (16; 1 for decode-only batches, which lets several CTAs share an SM)
-__host__ __device__ inline PfLayout pf_layout(int hpc, int gl, int H, int D, int DV, int stages, int prow, int kPfKeys) {
-    const int kPfPStride = kPfKeys + 8;
+__host__ __device__ inline PfLayout pf_layout(int hpc, int gl, int H, int D, int DV, int stages, int prow, int kPfKeys, int kPfPStride) {
     PfLayout l;
     int off = 0;
     l.k_off = off;
@@ -81,9 +80,9 @@ __device__ __forceinline__ float sigmoid_weight_fast(float dot, float scale, flo
 }
 
 template <int KMAX, int MAXWARPS, int kPfKeys>
-__global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(const atoma_sigmoid_attn_args a, int hpc, int gl, int cs, int splits,
+__global__ void __launch_bounds__(32 * MAXWARPS, (MAXWARPS == 8 && kPfKeys == 32) ? 2 : 1) sigmoid_attn_prefill_kernel(const atoma_sigmoid_attn_args a, int hpc, int gl, int cs, int splits,
                                                                              float *__restrict__ partial, int stages) {
-    constexpr int kPfPStride = kPfKeys + 8;
+    constexpr int kPfPStride = kPfKeys + ((MAXWARPS == 8 && kPfKeys == 32) ? 4 : 8);   // +4: two such CTAs fit an SM at 32 heads
     extern __shared__ __align__(16) unsigned char smem[];
     pdl_launch_dependents();
     pdl_wait();
@@ -106,7 +105,7 @@ __global__ void __launch_bounds__(32 * MAXWARPS) sigmoid_attn_prefill_kernel(con
     const int c = h / (H / G) - c_lo;                    // this warp's kv head among the staged ones
     const int nthreads = blockDim.x;
     const int prow = splits > 1 ? 1 : kPfRows;
-    const PfLayout L = pf_layout(hpc, gl, H, D, DV, stages, prow, kPfKeys);
+    const PfLayout L = pf_layout(hpc, gl, H, D, DV, stages, prow, kPfKeys, kPfPStride);
     __nv_bfloat16 *Ks0 = reinterpret_cast<__nv_bfloat16 *>(smem + L.k_off);
     __nv_bfloat16 *Vs0 = reinterpret_cast<__nv_bfloat16 *>(smem + L.v_off);
     const int k_stage = gl * kPfKeys * (D + 8), v_stage = gl * kPfKeys * (DV + 8);   // elements per stage
@@ -432,7 +431,7 @@ bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, b
         if (H % cand || H / cand > 8) continue;
         if (cand % rep != 0 && rep % cand != 0) continue;
         const int g = cand % rep == 0 ? cand / rep : 1;
-        if (pf_layout(cand, g, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 1, kPfRows, kPfKeysPrompt).total > 200 * 1024) continue;
+        if (pf_layout(cand, g, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 1, kPfRows, kPfKeysPrompt, kPfKeysPrompt + 8).total > 200 * 1024) continue;
         hpc = cand;
         gl = g;
         break;
@@ -457,13 +456,19 @@ bool hyb_attention_fast(const atoma_sigmoid_attn_args &a, cudaStream_t stream, b
     // two staging buffers (the next tile's copies fly during the math) whenever they fit
     // (measured at 32 heads of 128: one double-buffered CTA per SM beats two single-buffered ones, 8.1 vs 9.1 ms at 4k tokens)
     const int prow = splits > 1 ? 1 : kPfRows, keys = splits > 1 ? kPfKeysDecode : kPfKeysPrompt;
-    int stages = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 2, prow, keys).total <= 200 * 1024 ? 2 : 1;
-    PfLayout L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), stages, prow, keys);
+    const int pstride = keys + ((kmax > 64 && keys == kPfKeysPrompt) ? 4 : 8);
+    int stages = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 2, prow, keys, pstride).total <= 200 * 1024 ? 2 : 1;
+    if (splits == 1 && kmax > 64 && stages == 2) {   // 8-warp CTAs of 128 registers: two per SM when one staging buffer lets them fit
+        const int one = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 1, prow, keys, pstride).total + 1024;
+        const int two = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 2, prow, keys, pstride).total + 1024;
+        if (2 * one <= 227 * 1024 && 2 * two > 227 * 1024) stages = 1;
+    }
+    PfLayout L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), stages, prow, keys, pstride);
     if (L.total > 200 * 1024) {   // many kv heads per CTA at 64 keys: the decode-only batch runs as one-row tiles of 32 keys, unsplit
         splits = 1;
         partial = nullptr;
-        stages = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 2, kPfRows, kPfKeysPrompt).total <= 200 * 1024 ? 2 : 1;
-        L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), stages, kPfRows, kPfKeysPrompt);
+        stages = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), 2, kPfRows, kPfKeysPrompt, kPfKeysPrompt + ((kmax > 64) ? 4 : 8)).total <= 200 * 1024 ? 2 : 1;
+        L = pf_layout(hpc, gl, H, static_cast<int>(a.dim), static_cast<int>(a.vdim), stages, kPfRows, kPfKeysPrompt, kPfKeysPrompt + ((kmax > 64) ? 4 : 8));
     }
     cudaError_t e;
     if (splits > 1)
