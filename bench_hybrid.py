@@ -55,7 +55,7 @@ def _time(torch, fn, steps, warmup, flush=None):
 def _spec(torch, s):
     import math
     from atoma_infer_b200.hybrid import AttentionSpec, HybridSpec, LayerSpec, MinGruSpec, MlpSpec, slopes_power_of_two
-    att = AttentionSpec(s["heads"], s["kv_heads"], s["dim"], s["dim"], 1.0 / math.sqrt(s["dim"]), 50.0, 0.3, 128,
+    att = AttentionSpec(s["heads"], s["kv_heads"], s["dim"], s["dim"], 1.0 / math.sqrt(s["dim"]), 30.0, 0.25, 64,
                         tuple(slopes_power_of_two(s["heads"])))
     layers = []
     for i in range(s["layers"]):
@@ -63,7 +63,7 @@ def _spec(torch, s):
             layers.append(LayerSpec("mingru", mingru=MinGruSpec(s["state"]), mlp=MlpSpec(s["ff"], "relu")))
         else:
             layers.append(LayerSpec("attention", attention=att, mlp=MlpSpec(s["ff"], "relu")))
-    return HybridSpec(s["width"], s["vocab"], 1e-5, 0.5, tuple(layers))
+    return HybridSpec(s["width"], s["vocab"], 1e-6, 1.0, tuple(layers))
 
 
 def _weights(torch, spec, dev):
@@ -146,7 +146,7 @@ def _kernel_rows(torch, s, dev, steps, warmup, hbm, tf):
     slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device=dev)
     pb = torch.zeros(H, device=dev) - 1
     talk = torch.eye(H, device=dev) + 0.05
-    f = lambda: ho.sigmoid_attention_paged(q, kc, vc, pos, tseq, bt, slopes, pb, talk, H, G, D, D, page, 1 / math.sqrt(D), 50.0, S,
+    f = lambda: ho.sigmoid_attention_paged(q, kc, vc, pos, tseq, bt, slopes, pb, talk, H, G, D, D, page, 1 / math.sqrt(D), 30.0, S,
                                            query_start=qs, max_seq_len=S)
     ms = _time(torch, f, steps, warmup, flush)
     flops = 4.0 * H * D * S * (S + 1) / 2
@@ -166,7 +166,7 @@ def _kernel_rows(torch, s, dev, steps, warmup, hbm, tf):
     tseq = torch.arange(BATCH, device=dev, dtype=torch.int32)
     bt = torch.randperm(nb, device=dev).to(torch.int32).reshape(BATCH, mb)
     qs = torch.arange(BATCH + 1, device=dev, dtype=torch.int32)
-    f = lambda: ho.sigmoid_attention_paged(q, kc, vc, pos, tseq, bt, slopes, pb, talk, H, G, D, D, page, 1 / math.sqrt(D), 50.0, 1,
+    f = lambda: ho.sigmoid_attention_paged(q, kc, vc, pos, tseq, bt, slopes, pb, talk, H, G, D, D, page, 1 / math.sqrt(D), 30.0, 1,
                                            query_start=qs, max_seq_len=CTX + 1)
     ms = _time(torch, f, steps, warmup, flush)
     nbytes = BATCH * (CTX + 1) * G * 2 * D * 2
