@@ -169,7 +169,17 @@ class HybridLayer(C.Structure):
                                            "k_cache", "v_cache")] +
                 [("state_width", C.c_int64)] +
                 [(n, C.c_void_p) for n in ("w_zxg", "b_zxg", "state", "w_o")] +
-                [("ff", C.c_int64), ("act", C.c_int32), ("w_gate_up", C.c_void_p), ("w_down", C.c_void_p)])
+                [("ff", C.c_int64), ("act", C.c_int32), ("w_gate_up", C.c_void_p), ("w_down", C.c_void_p)] +
+                # pre-norm blocks: latent attention, gated residuals, mixture of experts, token side input
+                [(n, C.c_int64) for n in ("q_rank", "kv_rank", "window")] +
+                [(n, C.c_void_p) for n in ("w_down_in", "dq_norm", "dkv_norm", "sink", "w_uq", "w_uk", "w_uv", "latent_cache",
+                                           "gate1_bias", "gate2_bias")] +
+                [("ff_kind", C.c_int32), ("renormalize", C.c_int32)] +
+                [(n, C.c_int64) for n in ("experts", "top", "expert_ff")] +
+                [(n, C.c_float) for n in ("expert_limit", "shared_limit", "act_alpha", "act_up_shift")] +
+                [(n, C.c_void_p) for n in ("w_router", "w_shared_gate", "w_expert_gate_up", "w_expert_down", "w_ff_in")] +
+                [("side_part", C.c_int64)] +
+                [(n, C.c_void_p) for n in ("side_gate", "side_proj", "side_norm")])
 
 
 class HybridModel(C.Structure):
@@ -178,7 +188,34 @@ class HybridModel(C.Structure):
     _fields_ = ([(n, C.c_int64) for n in ("width", "vocab", "num_layers", "block_size")] +
                 [("eps", C.c_float), ("logit_scale", C.c_float), ("norm_offset", C.c_float), ("dtype", C.c_uint32)] +
                 [(n, C.c_void_p) for n in ("embed", "inv_freq", "final_norm", "head")] +
-                [("layers", C.POINTER(HybridLayer))])
+                [("layers", C.POINTER(HybridLayer))] +
+                [("block_style", C.c_int32), ("norm_groups", C.c_int32), ("pos_table", C.c_void_p), ("max_positions", C.c_int64),
+                 ("logit_softcap", C.c_float), ("side_table", C.c_void_p), ("side_dim", C.c_int64), ("side_table_width", C.c_int64)])
+
+
+class GatedResidualArgs(C.Structure):
+    """struct atoma_gated_residual_args"""
+
+    _fields_ = [("y", C.c_void_p), ("ld_y", C.c_int64), ("row_scale", C.c_void_p), ("expert_out", C.c_void_p), ("pair_row", C.c_void_p),
+                ("top", C.c_int64), ("gate", C.c_void_p), ("ld_gate", C.c_int64), ("gate_bias", C.c_void_p), ("x", C.c_void_p),
+                ("w_next", C.c_void_p), ("h", C.c_void_p), ("x_cast", C.c_void_p), ("T", C.c_int64), ("width", C.c_int64),
+                ("groups", C.c_int64), ("eps", C.c_float), ("weight_offset", C.c_float), ("dtype", C.c_uint32)]
+
+
+class LatentAttnArgs(C.Structure):
+    """struct atoma_latent_attn_args"""
+
+    _fields_ = ([(n, C.c_void_p) for n in ("q_lat", "latent_cache", "out", "positions", "token_seq", "query_start", "block_tables", "sink")] +
+                [(n, C.c_int64) for n in ("T", "B", "max_blocks", "H", "R", "block_size", "window")] +
+                [("scale", C.c_float), ("dtype", C.c_uint32), ("max_query_len", C.c_int32), ("max_seq_len", C.c_int32)])
+
+
+class MoeArgs(C.Structure):
+    """struct atoma_moe_args"""
+
+    _fields_ = ([(n, C.c_void_p) for n in ("h", "top_expert", "top_weight", "w_gate_up", "w_down", "workspace")] +
+                [(n, C.c_int64) for n in ("workspace_bytes", "T", "width", "experts", "top", "ff")] +
+                [(n, C.c_float) for n in ("limit", "alpha", "up_shift")] + [("scale_input", C.c_int32), ("dtype", C.c_uint32)])
 
 
 class HybridBatch(C.Structure):
@@ -293,6 +330,22 @@ SIGNATURES = {
     "atoma_glu": (None, [C.c_void_p] * 2 + [C.c_int64] * 2 + [C.c_int32, C.c_uint32, C.c_void_p]),
     "atoma_linear": (None, [C.c_void_p] * 3 + [C.c_int64] * 3 + [C.c_uint32, C.c_void_p]),
     "atoma_scale_logits_greedy": (None, [C.c_void_p] * 3 + [C.c_int64] * 2 + [C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_embed_learned": (None, [C.c_void_p] * 5 + [C.c_int64] * 4 + [C.c_uint32, C.c_void_p]),
+    "atoma_group_rmsnorm_rows": (None, [C.c_void_p] * 3 + [C.c_float, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_uint32,
+                                        C.c_void_p]),
+    "atoma_gated_residual_norm": (None, [C.POINTER(GatedResidualArgs), C.c_void_p]),
+    "atoma_side_gate": (None, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_int64,
+                               C.c_int64, C.c_uint32, C.c_void_p]),
+    "atoma_unitnorm_add_norm": (None, [C.c_void_p] * 5 + [C.c_int64] * 3 + [C.c_float, C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_latent_norm_cache": (None, [C.c_void_p, C.c_int64] + [C.c_void_p] * 5 + [C.c_int64] * 3 + [C.c_float, C.c_uint32, C.c_void_p]),
+    "atoma_head_project": (None, [C.c_void_p] * 3 + [C.c_int64] * 4 + [C.c_int32, C.c_uint32, C.c_void_p]),
+    "atoma_latent_attention_paged": (None, [C.POINTER(LatentAttnArgs), C.c_void_p]),
+    "atoma_moe_route": (None, [C.c_void_p] * 6 + [C.c_int64] * 4 + [C.c_int32, C.c_uint32, C.c_void_p]),
+    "atoma_glu_clamped": (None, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_uint32,
+                                 C.c_void_p]),
+    "atoma_moe_workspace_bytes": (C.c_int64, [C.c_int64] * 5 + [C.c_uint32]),
+    "atoma_moe_experts": (None, [C.POINTER(MoeArgs), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p]),
+    "atoma_finish_logits_greedy": (None, [C.c_void_p] * 3 + [C.c_int64] * 2 + [C.c_float, C.c_float, C.c_uint32, C.c_void_p]),
     "atoma_hybrid_abi_sizeof": (C.c_int64, [C.c_int]),
     "atoma_hybrid_scratch_bytes": (C.c_int64, [C.POINTER(HybridModel), C.c_int64, C.c_int64]),
     "atoma_hybrid_step": (None, [C.POINTER(HybridModel), C.POINTER(HybridBatch), C.c_void_p]),

@@ -55,5 +55,31 @@ __device__ __forceinline__ float glu_act(float g, int act) {
     return silu(g);
 }
 
+// Clamped gated activation: g = min(g, limit), u = clamp(u, -limit, limit) (limit <= 0: no clamp); g sigmoid(alpha g) (u + shift).
+__device__ __forceinline__ float glu_clamped(float g, float u, float limit, float alpha, float shift) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    return g * sigmoidf_(alpha * g) * (u + shift);
+}
+
+__device__ __forceinline__ float gelu_tanh(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+
+// Host side: what every operator does after a launch, and the number-format check.
+inline bool launched(cudaError_t e, const char *what) {
+    note_launch();
+    if (e != cudaSuccess) {
+        set_status(static_cast<int>(e), "%s: %s", what, cudaGetErrorString(e));
+        return false;
+    }
+    return check_launch(what);
+}
+inline bool known_dtype(uint32_t dtype, const char *what) {
+    if (dtype == 1u || dtype == 2u) return true;
+    set_status(kErrInvalidArg, "%s: dtype must be 1 (bfloat16) or 2 (float32), got %u", what, dtype);
+    return false;
+}
+
 }  // namespace hybrid
 }  // namespace atoma

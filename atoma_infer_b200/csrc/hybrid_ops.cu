@@ -437,7 +437,8 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(const T *__restrict__ x
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) scale_greedy_kernel(const T *__restrict__ logits, float *__restrict__ out,
-                                                           uint32_t *__restrict__ token_out, int vocab, float scale) {
+                                                           uint32_t *__restrict__ token_out, int vocab, float scale,
+                                                           float softcap) {
     __shared__ float bv[256];
     __shared__ int bi[256];
     pdl_launch_dependents();
@@ -446,7 +447,8 @@ __global__ void __launch_bounds__(256) scale_greedy_kernel(const T *__restrict__
     float best = -INFINITY;
     int idx = -1;
     for (int c = threadIdx.x; c < vocab; c += blockDim.x) {
-        const float v = to_f(logits[base + c]) * scale;
+        float v = to_f(logits[base + c]) * scale;
+        if (softcap > 0.f) v = softcap * tanhf(v / softcap);
         if (out) out[base + c] = v;
         if (v >= best) {
             best = v;
@@ -692,8 +694,8 @@ bool hyb_gate_up_act(const void *x, const void *w_gate_up, void *proj, void *act
     return hyb_glu(proj, act_out, T, ff, act, dtype, stream);
 }
 
-bool hyb_scale_greedy(const void *logits, float *out, uint32_t *token_out, int64_t R, int64_t vocab, float scale, uint32_t dtype,
-                      cudaStream_t stream) {
+bool hyb_scale_greedy(const void *logits, float *out, uint32_t *token_out, int64_t R, int64_t vocab, float scale, float softcap,
+                      uint32_t dtype, cudaStream_t stream) {
     if (R <= 0) return true;
     if (bad_dtype(dtype, "atoma_scale_logits_greedy")) return false;
     if (!logits || vocab <= 0) {
@@ -701,7 +703,7 @@ bool hyb_scale_greedy(const void *logits, float *out, uint32_t *token_out, int64
         return false;
     }
 #define CALL(TT) launch_ex(scale_greedy_kernel<TT>, dim3(static_cast<unsigned>(R)), dim3(256), 0, stream, \
-                           static_cast<const TT *>(logits), out, token_out, static_cast<int>(vocab), scale)
+                           static_cast<const TT *>(logits), out, token_out, static_cast<int>(vocab), scale, softcap)
     return finish(HYB_DISPATCH(dtype, CALL), "scale_greedy_kernel");
 #undef CALL
 }
@@ -760,6 +762,11 @@ extern "C" void atoma_linear(const void *x, const void *w, void *y, int64_t T, i
 extern "C" void atoma_scale_logits_greedy(const void *logits, float *logits_f32, uint32_t *token_out, int64_t R, int64_t vocab,
                                           float scale, uint32_t dtype, atoma_stream_t stream) {
     clear_status();
-    hyb_scale_greedy(logits, logits_f32, token_out, R, vocab, scale, dtype, static_cast<cudaStream_t>(stream));
+    hyb_scale_greedy(logits, logits_f32, token_out, R, vocab, scale, 0.f, dtype, static_cast<cudaStream_t>(stream));
+}
+extern "C" void atoma_finish_logits_greedy(const void *logits, float *logits_f32, uint32_t *token_out, int64_t R, int64_t vocab, float scale,
+                                           float softcap, uint32_t dtype, atoma_stream_t stream) {
+    clear_status();
+    hyb_scale_greedy(logits, logits_f32, token_out, R, vocab, scale, softcap, dtype, static_cast<cudaStream_t>(stream));
 }
 extern "C" void atoma_debug_hybrid(int flags) { g_hybrid_debug = flags; }

@@ -30,7 +30,25 @@ bool hyb_mingru_scan(const void *, const float *, float *, const int32_t *, cons
 bool hyb_glu(const void *, void *, int64_t, int64_t, int32_t, uint32_t, cudaStream_t);
 bool hyb_gate_up_act(const void *, const void *, void *, void *, int64_t, int64_t, int64_t, int32_t, uint32_t, cudaStream_t);
 bool hyb_linear(const void *, const void *, void *, int64_t, int64_t, int64_t, uint32_t, cudaStream_t);
-bool hyb_scale_greedy(const void *, float *, uint32_t *, int64_t, int64_t, float, uint32_t, cudaStream_t);
+bool hyb_scale_greedy(const void *, float *, uint32_t *, int64_t, int64_t, float, float, uint32_t, cudaStream_t);
+bool hyb_embed_learned(const uint32_t *, const int64_t *, const void *, const void *, float *, int64_t, int64_t, int64_t, int64_t, uint32_t,
+                       cudaStream_t);
+bool hyb_group_rmsnorm_rows(const float *, const int32_t *, const float *, float, int64_t, void *, int64_t, int64_t, float, uint32_t,
+                            cudaStream_t);
+bool hyb_gated_residual_norm(const atoma_gated_residual_args &, cudaStream_t);
+bool hyb_side_gate(const void *, int64_t, const uint32_t *, const void *, int64_t, int64_t, void *, int64_t, int64_t, int64_t, uint32_t,
+                   cudaStream_t);
+bool hyb_unitnorm_add_norm(const void *, float *, const float *, const float *, void *, int64_t, int64_t, int64_t, float, float, uint32_t,
+                           cudaStream_t);
+bool hyb_glu_clamped(const void *, int64_t, void *, int64_t, int64_t, float, float, float, uint32_t, cudaStream_t);
+bool hyb_latent_norm_cache(const void *, int64_t, const float *, const float *, const int64_t *, void *, void *, int64_t, int64_t, int64_t,
+                           float, uint32_t, cudaStream_t);
+bool hyb_head_project(const void *, const void *, void *, int64_t, int64_t, int64_t, int64_t, int32_t, uint32_t, cudaStream_t);
+bool hyb_latent_attention(const atoma_latent_attn_args &, cudaStream_t);
+bool hyb_moe_route(const void *, const float *, const float *, int32_t *, float *, float *, int64_t, int64_t, int64_t, int64_t, int32_t,
+                   uint32_t, cudaStream_t);
+int64_t hyb_moe_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t, uint32_t);
+bool hyb_moe_experts(const atoma_moe_args &, const void **, const int32_t **, cudaStream_t);
 
 namespace {
 
@@ -38,12 +56,33 @@ inline int64_t up256(int64_t x) { return (x + 255) / 256 * 256; }
 
 struct Widths {
     int64_t proj = 0, q = 0, act = 0;   // widest projection output, query row, mixer / feed-forward activation row
+    int64_t cq = 0, lat = 0, route = 0, side = 0;   // query latent row, heads x latent row, router outputs per token, side input row
+    int64_t moe = 0;                    // bytes of the routed experts' workspace
 };
 
-Widths widths(const atoma_hybrid_model &m) {
+inline bool gated(const float *bias) { return bias != nullptr; }
+
+Widths widths(const atoma_hybrid_model &m, int64_t T) {
     Widths w;
     for (int64_t i = 0; i < m.num_layers; ++i) {
         const atoma_hybrid_layer &l = m.layers[i];
+        if (l.mixer == ATOMA_MIXER_LATENT_ATTENTION) {
+            w.proj = std::max(w.proj, l.q_rank + l.kv_rank + (gated(l.gate1_bias) ? m.width : 0));
+            w.q = std::max(w.q, l.heads * l.dim);
+            w.act = std::max(w.act, l.heads * l.vdim);
+            w.cq = std::max(w.cq, l.q_rank);
+            w.lat = std::max(w.lat, l.heads * l.kv_rank);
+            if (l.has_mlp) {
+                w.proj = std::max(w.proj, 2 * l.ff + (gated(l.gate2_bias) ? m.width : 0));
+                w.act = std::max(w.act, l.ff);
+                if (l.ff_kind == ATOMA_FF_MOE) {
+                    w.route = std::max(w.route, l.top);
+                    w.moe = std::max(w.moe, hyb_moe_workspace_bytes(T, l.top, l.experts, m.width, l.expert_ff, m.dtype));
+                }
+            }
+            if (l.side_gate) w.side = std::max(w.side, m.side_dim);
+            continue;
+        }
         if (l.mixer == ATOMA_MIXER_SIGMOID_ATTENTION) {
             w.proj = std::max(w.proj, (l.heads + l.kv_heads) * l.dim + l.kv_heads * l.vdim);
             w.q = std::max(w.q, l.heads * l.dim);
@@ -63,12 +102,17 @@ Widths widths(const atoma_hybrid_model &m) {
 struct Scratch {
     float *x;
     char *h, *proj, *q, *act, *y, *hs, *lg;
+    // pre-norm designs
+    char *cq, *xc, *side_a, *side_g, *moe;
+    float *qlat, *olat, *top_weight, *row_gate;
+    int32_t *top_expert;
+    int64_t moe_bytes;
     int64_t total;
 };
 
 Scratch carve(const atoma_hybrid_model &m, int64_t T, int64_t S, void *base) {
     const int64_t es = m.dtype == ATOMA_DTYPE_F32 ? 4 : 2;
-    const Widths w = widths(m);
+    const Widths w = widths(m, T);
     Scratch s{};
     int64_t off = 0;
     char *b = static_cast<char *>(base);
@@ -85,8 +129,155 @@ Scratch carve(const atoma_hybrid_model &m, int64_t T, int64_t S, void *base) {
     s.y = take(T * m.width * es);
     s.hs = take(S * m.width * es);
     s.lg = take(S * m.vocab * es);
+    s.cq = take(T * w.cq * es);
+    s.qlat = reinterpret_cast<float *>(take(T * w.lat * 4));
+    s.olat = reinterpret_cast<float *>(take(T * w.lat * 4));
+    s.top_expert = reinterpret_cast<int32_t *>(take(T * w.route * 4));
+    s.top_weight = reinterpret_cast<float *>(take(T * w.route * 4));
+    s.row_gate = reinterpret_cast<float *>(take(T * 4));
+    s.xc = take(w.side ? T * m.width * es : 0);
+    s.side_a = take(T * w.side * es);
+    s.side_g = take(T * w.side * es);
+    s.moe = take(w.moe);
+    s.moe_bytes = w.moe;
     s.total = off;
     return s;
+}
+
+// One layer of a pre-norm design: x += gate1 * mixer(norm1 x); x += gate2 * ff(norm2 x); x += unit-normed side input.
+// s.h holds norm1(x) on entry and the next layer's norm1(x) (next_norm, may be NULL) on return.
+bool prenorm_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, const atoma_hybrid_layer &l, const Scratch &s,
+                   const float *next_norm, cudaStream_t stream) {
+    const uint32_t dt = m.dtype;
+    const int64_t es = dt == ATOMA_DTYPE_F32 ? 4 : 2;
+    const int64_t T = b.num_tokens, W = m.width;
+    const int64_t groups = m.norm_groups > 0 ? m.norm_groups : 1;
+    const float off = m.norm_offset;
+    if (l.mixer != ATOMA_MIXER_LATENT_ATTENTION) {
+        set_status(kErrUnsupported, "atoma_hybrid_step: pre-norm layers take the latent-attention mixer, got %d", l.mixer);
+        return false;
+    }
+    // ---- mixer: one product makes the query latent, the key/value latent and the residual gate ----
+    const int64_t n_in = l.q_rank + l.kv_rank + (gated(l.gate1_bias) ? W : 0);
+    if (!hyb_linear(s.h, l.w_down_in, s.proj, T, n_in, W, dt, stream)) return false;
+    if (!hyb_latent_norm_cache(s.proj, n_in, l.dq_norm, l.dkv_norm, b.slot_mapping, s.cq, l.latent_cache, T, l.q_rank, l.kv_rank, m.eps, dt,
+                               stream))
+        return false;
+    if (!hyb_linear(s.cq, l.w_uq, s.q, T, l.heads * l.dim, l.q_rank, dt, stream)) return false;
+    if (!hyb_head_project(s.q, l.w_uk, s.qlat, T, l.heads, l.dim, l.kv_rank, 1, dt, stream)) return false;
+    atoma_latent_attn_args a{};
+    a.q_lat = s.qlat;
+    a.latent_cache = l.latent_cache;
+    a.out = s.olat;
+    a.positions = b.positions;
+    a.token_seq = b.token_seq;
+    a.query_start = b.query_start;
+    a.block_tables = b.block_tables;
+    a.sink = l.sink;
+    a.T = T;
+    a.B = b.num_seqs;
+    a.max_blocks = b.max_blocks;
+    a.H = l.heads;
+    a.R = l.kv_rank;
+    a.block_size = m.block_size;
+    a.window = l.window;
+    a.scale = l.scale;
+    a.dtype = dt;
+    a.max_query_len = b.max_query_len;
+    a.max_seq_len = b.max_seq_len;
+    if (!hyb_latent_attention(a, stream)) return false;
+    if (!hyb_head_project(s.olat, l.w_uv, s.act, T, l.heads, l.vdim, l.kv_rank, 0, dt, stream)) return false;
+    if (!hyb_linear(s.act, l.w_o, s.y, T, W, l.heads * l.vdim, dt, stream)) return false;
+    const bool side = l.side_gate != nullptr;
+    atoma_gated_residual_args r{};
+    r.y = s.y;
+    r.ld_y = W;
+    r.gate = gated(l.gate1_bias) ? s.proj + (l.q_rank + l.kv_rank) * es : nullptr;
+    r.ld_gate = n_in;
+    r.gate_bias = l.gate1_bias;
+    r.x = s.x;
+    r.w_next = l.has_mlp ? l.norm2 : (side ? nullptr : next_norm);
+    r.h = s.h;
+    r.x_cast = (!l.has_mlp && side) ? s.xc : nullptr;
+    r.T = T;
+    r.width = W;
+    r.groups = groups;
+    r.eps = m.eps;
+    r.weight_offset = off;
+    r.dtype = dt;
+    if (!hyb_gated_residual_norm(r, stream)) return false;
+    // ---- feed-forward ----
+    if (l.has_mlp) {
+        atoma_gated_residual_args f{};
+        const int64_t n_ff = 2 * l.ff + (gated(l.gate2_bias) ? W : 0);
+        if (n_ff > 0 && !hyb_linear(s.h, l.w_ff_in, s.proj, T, n_ff, W, dt, stream)) return false;
+        if (l.ff > 0) {   // the dense (or shared) expert
+            const float limit = l.ff_kind == ATOMA_FF_MOE ? l.shared_limit : l.expert_limit;
+            if (!hyb_glu_clamped(s.proj, n_ff, s.act, T, l.ff, limit, l.act_alpha, l.act_up_shift, dt, stream)) return false;
+            if (!hyb_linear(s.act, l.w_down, s.y, T, W, l.ff, dt, stream)) return false;
+            f.y = s.y;
+            f.ld_y = W;
+        }
+        if (l.ff_kind == ATOMA_FF_MOE) {
+            const bool row_gate = l.ff > 0 && l.w_shared_gate;
+            if (!hyb_moe_route(s.h, l.w_router, row_gate ? l.w_shared_gate : nullptr, s.top_expert, s.top_weight, s.row_gate, T, W,
+                               l.experts, l.top, l.renormalize, dt, stream))
+                return false;
+            atoma_moe_args e{};
+            e.h = s.h;
+            e.top_expert = s.top_expert;
+            e.top_weight = s.top_weight;
+            e.w_gate_up = l.w_expert_gate_up;
+            e.w_down = l.w_expert_down;
+            e.workspace = s.moe;
+            e.workspace_bytes = s.moe_bytes;
+            e.T = T;
+            e.width = W;
+            e.experts = l.experts;
+            e.top = l.top;
+            e.ff = l.expert_ff;
+            e.limit = l.expert_limit;
+            e.alpha = l.act_alpha;
+            e.up_shift = l.act_up_shift;
+            e.scale_input = 1;
+            e.dtype = dt;
+            const void *eo = nullptr;
+            const int32_t *pr = nullptr;
+            if (!hyb_moe_experts(e, &eo, &pr, stream)) return false;
+            f.expert_out = eo;
+            f.pair_row = pr;
+            f.top = l.top;
+            if (row_gate) f.row_scale = s.row_gate;
+        }
+        f.gate = gated(l.gate2_bias) ? s.proj + 2 * l.ff * es : nullptr;
+        f.ld_gate = n_ff;
+        f.gate_bias = l.gate2_bias;
+        f.x = s.x;
+        f.w_next = side ? nullptr : next_norm;
+        f.h = s.h;
+        f.x_cast = side ? s.xc : nullptr;
+        f.T = T;
+        f.width = W;
+        f.groups = groups;
+        f.eps = m.eps;
+        f.weight_offset = off;
+        f.dtype = dt;
+        if (!hyb_gated_residual_norm(f, stream)) return false;
+    }
+    // ---- token side input ----
+    if (side) {
+        const int64_t D = m.side_dim;
+        if (!m.side_table || D <= 0 || !l.side_proj || !l.side_norm) {
+            set_status(kErrInvalidArg, "atoma_hybrid_step: a layer has a side input but the model has no side table");
+            return false;
+        }
+        if (!hyb_linear(s.xc, l.side_gate, s.side_a, T, D, W, dt, stream)) return false;
+        if (!hyb_side_gate(s.side_a, D, b.tokens, m.side_table, m.side_table_width, l.side_part, s.side_g, T, D, m.vocab, dt, stream))
+            return false;
+        if (!hyb_linear(s.side_g, l.side_proj, s.y, T, W, D, dt, stream)) return false;
+        if (!hyb_unitnorm_add_norm(s.y, s.x, l.side_norm, next_norm, s.h, T, W, groups, m.eps, off, dt, stream)) return false;
+    }
+    return true;
 }
 
 }  // namespace
@@ -100,6 +291,9 @@ extern "C" int64_t atoma_hybrid_abi_sizeof(int which) {
         case 1: return sizeof(atoma_hybrid_model);
         case 2: return sizeof(atoma_hybrid_batch);
         case 3: return sizeof(atoma_sigmoid_attn_args);
+        case 4: return sizeof(atoma_gated_residual_args);
+        case 5: return sizeof(atoma_latent_attn_args);
+        case 6: return sizeof(atoma_moe_args);
         default: return -1;
     }
 }
@@ -121,7 +315,7 @@ extern "C" void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_h
     const int64_t T = b.num_tokens, B = b.num_seqs, S = b.num_selected;
     if (T <= 0 || B <= 0) return;
     if (!b.tokens || !b.positions || !b.slot_mapping || !b.token_seq || !b.query_start || !b.context_lens || !b.block_tables ||
-        !b.state_slots || !b.scratch || (S > 0 && (!b.selected || !b.logits)) || !m.embed || !m.inv_freq || !m.final_norm ||
+        !b.state_slots || !b.scratch || (S > 0 && (!b.selected || !b.logits)) || !m.embed || (!m.inv_freq && !m.pos_table) || !m.final_norm ||
         !m.head || m.width <= 0 || m.vocab <= 0 || m.num_layers <= 0) {
         set_status(kErrInvalidArg, "atoma_hybrid_step: a required tensor is NULL");
         return;
@@ -139,11 +333,22 @@ extern "C" void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_h
     const uint32_t dt = m.dtype;
     const int64_t W = m.width;
     const float off = m.norm_offset;
-    if (!hyb_embed_sinusoid(b.tokens, b.positions, m.embed, m.inv_freq, s.x, T, W, m.vocab, dt, stream)) return;
-    if (!hyb_rmsnorm_rows(s.x, nullptr, m.layers[0].norm1, off, s.h, T, W, m.eps, dt, stream)) return;
+    const int64_t groups = m.norm_groups > 0 ? m.norm_groups : 1;
+    if (m.pos_table) {
+        if (!hyb_embed_learned(b.tokens, b.positions, m.embed, m.pos_table, s.x, T, W, m.vocab, m.max_positions, dt, stream)) return;
+    } else if (!hyb_embed_sinusoid(b.tokens, b.positions, m.embed, m.inv_freq, s.x, T, W, m.vocab, dt, stream)) {
+        return;
+    }
+    if (!hyb_group_rmsnorm_rows(s.x, nullptr, m.layers[0].norm1, off, groups, s.h, T, W, m.eps, dt, stream)) return;
     for (int64_t i = 0; i < m.num_layers; ++i) {
         const atoma_hybrid_layer &l = m.layers[i];
         const float *next_norm = i + 1 < m.num_layers ? m.layers[i + 1].norm1 : nullptr;
+        if (m.block_style == ATOMA_BLOCK_PRENORM) {
+            if (!prenorm_layer(m, b, l, s, next_norm, stream)) return;
+            if (b.residual_trace)
+                cudaMemcpyAsync(b.residual_trace + i * T * W, s.x, static_cast<size_t>(T) * W * 4, cudaMemcpyDeviceToDevice, stream);
+            continue;
+        }
         if (l.mixer == ATOMA_MIXER_SIGMOID_ATTENTION) {
             const int64_t nqkv = (l.heads + l.kv_heads) * l.dim + l.kv_heads * l.vdim;
             if (!hyb_linear(s.h, l.w_qkv, s.proj, T, nqkv, W, dt, stream)) return;
@@ -199,8 +404,8 @@ extern "C" void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_h
         }
     }
     if (S > 0) {
-        if (!hyb_rmsnorm_rows(s.x, b.selected, m.final_norm, off, s.hs, S, W, m.eps, dt, stream)) return;
+        if (!hyb_group_rmsnorm_rows(s.x, b.selected, m.final_norm, off, groups, s.hs, S, W, m.eps, dt, stream)) return;
         if (!hyb_linear(s.hs, m.head, s.lg, S, m.vocab, W, dt, stream)) return;
-        if (!hyb_scale_greedy(s.lg, b.logits, b.next_tokens, S, m.vocab, m.logit_scale, dt, stream)) return;
+        if (!hyb_scale_greedy(s.lg, b.logits, b.next_tokens, S, m.vocab, m.logit_scale, m.logit_softcap, dt, stream)) return;
     }
 }

@@ -1,0 +1,339 @@
+// Mixture-of-experts feed-forward on a mixed batch — include/atoma_hybrid.h.
+//
+// Router in float32 (one CTA per token: dot products, the score function, the `top` largest), then the routed
+// experts without a host read: the (token, k) pairs are sorted by expert on the device into segments padded to
+// whole row tiles, the pairs' input rows are gathered (scaled by the router's weight when the design scales the
+// expert's input), and two grouped products run over the row tiles — gate/up with the clamped gated activation in
+// the epilogue, then down.  A row's arithmetic does not depend on which tile or segment position it lands in,
+// so a token's result is independent of the batch around it.  The token's rows are summed, in the order of k,
+// by the residual kernel (atoma_gated_residual_norm).
+#include "common.cuh"
+#include "hybrid_common.cuh"
+
+#include "atoma_hybrid.h"
+
+#include <algorithm>
+
+namespace atoma {
+namespace {
+
+using namespace hybrid;
+
+constexpr int kTileRows = 64;
+constexpr int kMaxExperts = 1024;
+
+// ---------------------------------------------------------------------------------------------
+// router
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128) moe_route_kernel(const T *__restrict__ h, const float *__restrict__ w_router,
+                                                        const float *__restrict__ w_row_gate, int32_t *__restrict__ top_expert,
+                                                        float *__restrict__ top_weight, float *__restrict__ row_gate, int width,
+                                                        int experts, int top, int renormalize) {
+    __shared__ float z_s[kMaxExperts + 1];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int64_t t = blockIdx.x;
+    const T *hr = h + t * width;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    const int rows = experts + (w_row_gate ? 1 : 0);
+    for (int e = warp; e < rows; e += nwarp) {
+        const float *wr = e < experts ? w_router + static_cast<int64_t>(e) * width : w_row_gate;
+        float dot = 0.f;
+        for (int c = lane; c < width; c += 32) dot = fmaf(to_f(hr[c]), wr[c], dot);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (lane == 0) z_s[e] = dot;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (w_row_gate && lane == 0) row_gate[t] = sigmoidf_(z_s[experts]);
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int idx = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float z = z_s[e];
+            if (z > best) {   // ascending e: the lower index wins a tie
+                best = z;
+                idx = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ob > best || (ob == best && oi < idx)) {
+                best = ob;
+                idx = oi;
+            }
+        }
+        const float s = sigmoidf_(best);
+        total += s;
+        if (lane == 0) {
+            top_expert[t * top + k] = idx;
+            top_weight[t * top + k] = s;
+            z_s[idx] = -INFINITY;   // taken
+        }
+        __syncwarp();
+    }
+    if (renormalize && lane == 0)
+        for (int k = 0; k < top; ++k) top_weight[t * top + k] /= total;
+}
+
+// ---------------------------------------------------------------------------------------------
+// pairs -> expert segments (one CTA)
+// meta[0] = row tiles in use, meta[1] = rows in use (padded)
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t *__restrict__ top_expert, int32_t *__restrict__ pair_row,
+                                                        int32_t *__restrict__ row_pair, int32_t *__restrict__ tile_expert,
+                                                        int32_t *__restrict__ meta, int pairs, int experts, int max_rows) {
+    __shared__ int count[kMaxExperts], base[kMaxExperts];
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+    for (int r = threadIdx.x; r < max_rows; r += blockDim.x) row_pair[r] = -1;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = top_expert[i];
+        if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int row = 0;
+        for (int e = 0; e < experts; ++e) {
+            base[e] = row;
+            const int tiles = (count[e] + kTileRows - 1) / kTileRows;
+            for (int i = 0; i < tiles; ++i) tile_expert[row / kTileRows + i] = e;
+            row += tiles * kTileRows;
+            count[e] = 0;   // reused as the segment's cursor
+        }
+        meta[0] = row / kTileRows;
+        meta[1] = row;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = top_expert[i];
+        if (e < 0 || e >= experts) {
+            pair_row[i] = 0;
+            continue;
+        }
+        const int r = base[e] + atomicAdd(&count[e], 1);
+        pair_row[i] = r;
+        row_pair[r] = i;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) moe_gather_kernel(const T *__restrict__ h, const float *__restrict__ top_weight,
+                                                         const int32_t *__restrict__ row_pair, const int32_t *__restrict__ meta,
+                                                         T *__restrict__ xs, int width, int top, int scale_input) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x;
+    if (row >= meta[1]) return;
+    const int pair = row_pair[row];
+    T *o = xs + static_cast<int64_t>(row) * width;
+    if (pair < 0) {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = from_f<T>(0.f);
+        return;
+    }
+    const float w = scale_input ? top_weight[pair] : 1.f;
+    const T *src = h + static_cast<int64_t>(pair / top) * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = from_f<T>(to_f(src[c]) * w);
+}
+
+// ---------------------------------------------------------------------------------------------
+// grouped products over row tiles: float32 FMA, k ascending
+// GLU = true:  out[row, n] = act(x w_gate[n]^T, x w_up[n]^T), weights of expert e at w + e * 2 N K (gate rows, up rows)
+// GLU = false: out[row, n] = x w[n]^T (* the pair's router weight when out_weight), weights of expert e at w + e * N K
+// ---------------------------------------------------------------------------------------------
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(256) moe_grouped_kernel(const T *__restrict__ x, const T *__restrict__ w, T *__restrict__ out,
+                                                          const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ meta,
+                                                          const int32_t *__restrict__ row_pair, const float *__restrict__ out_weight,
+                                                          int N, int K, float limit, float alpha, float shift) {
+    __shared__ float xs[16][65], ws[16][65], us[GLU ? 16 : 1][65];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tile = blockIdx.y;
+    if (tile >= meta[0]) return;
+    const int64_t e = tile_expert[tile];
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    const int m0 = tile * kTileRows, n0 = blockIdx.x * 64;
+    const T *wg = w + e * (GLU ? 2 : 1) * N * K;
+    const T *wu = wg + static_cast<int64_t>(N) * K;
+    float acc[4][4] = {}, acu[GLU ? 4 : 1][4] = {};
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+            const int r = i / 16, k = i % 16;
+            const bool kin = k0 + k < K, nin = n0 + r < N;
+            xs[k][r] = kin ? to_f(x[static_cast<int64_t>(m0 + r) * K + k0 + k]) : 0.f;
+            ws[k][r] = (kin && nin) ? to_f(wg[static_cast<int64_t>(n0 + r) * K + k0 + k]) : 0.f;
+            if constexpr (GLU) us[k][r] = (kin && nin) ? to_f(wu[static_cast<int64_t>(n0 + r) * K + k0 + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            float xv[4], wv[4], uv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                xv[i] = xs[k][ty * 4 + i];
+                wv[i] = ws[k][tx * 4 + i];
+                if constexpr (GLU) uv[i] = us[k][tx * 4 + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+                    if constexpr (GLU) acu[i][j] = fmaf(xv[i], uv[j], acu[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        float ow = 1.f;
+        if (!GLU && out_weight != nullptr) {
+            const int pair = row_pair[m];
+            ow = pair >= 0 ? out_weight[pair] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v;
+            if constexpr (GLU) v = glu_clamped(acc[i][j], acu[i][j], limit, alpha, shift);
+            else v = acc[i][j] * ow;
+            out[static_cast<int64_t>(m) * N + n] = from_f<T>(v);
+        }
+    }
+}
+
+inline int64_t up256(int64_t x) { return (x + 255) / 256 * 256; }
+
+struct MoeSpace {
+    int32_t *pair_row, *row_pair, *tile_expert, *meta;
+    char *xs, *act, *y;
+    int64_t max_tiles, max_rows, total;
+};
+
+MoeSpace carve(int64_t T, int64_t top, int64_t experts, int64_t width, int64_t ff, uint32_t dtype, void *base) {
+    const int64_t es = dtype == ATOMA_DTYPE_F32 ? 4 : 2;
+    MoeSpace s{};
+    const int64_t pairs = T * top;
+    s.max_tiles = std::min<int64_t>((pairs + kTileRows - 1) / kTileRows + experts, pairs);   // every tile in use holds a pair
+    s.max_rows = s.max_tiles * kTileRows;
+    int64_t off = 0;
+    char *b = static_cast<char *>(base);
+    auto take = [&](int64_t bytes) {
+        char *p = b ? b + off : nullptr;
+        off += up256(bytes);
+        return p;
+    };
+    s.pair_row = reinterpret_cast<int32_t *>(take(pairs * 4));
+    s.row_pair = reinterpret_cast<int32_t *>(take(s.max_rows * 4));
+    s.tile_expert = reinterpret_cast<int32_t *>(take(s.max_tiles * 4));
+    s.meta = reinterpret_cast<int32_t *>(take(16));
+    s.xs = take(s.max_rows * width * es);
+    s.act = take(s.max_rows * ff * es);
+    s.y = take(s.max_rows * width * es);
+    s.total = off;
+    return s;
+}
+
+}  // namespace
+
+#define HYB_DISPATCH(dtype, CALL) ((dtype) == ATOMA_DTYPE_BF16 ? CALL(__nv_bfloat16) : CALL(float))
+
+bool hyb_moe_route(const void *h, const float *w_router, const float *w_row_gate, int32_t *top_expert, float *top_weight, float *row_gate,
+                   int64_t T, int64_t width, int64_t experts, int64_t top, int32_t renormalize, uint32_t dtype, cudaStream_t stream) {
+    if (T <= 0) return true;
+    if (!hybrid::known_dtype(dtype, "atoma_moe_route")) return false;
+    if (!h || !w_router || !top_expert || !top_weight || (w_row_gate && !row_gate) || width <= 0 || experts <= 0 || experts > kMaxExperts ||
+        top <= 0 || top > experts) {
+        set_status(kErrInvalidArg, "atoma_moe_route: null argument, or top %lld of %lld experts (at most %d experts)",
+                   static_cast<long long>(top), static_cast<long long>(experts), kMaxExperts);
+        return false;
+    }
+#define CALL(TT) launch_ex(moe_route_kernel<TT>, dim3(static_cast<unsigned>(T)), dim3(128), 0, stream, static_cast<const TT *>(h), w_router, \
+                           w_row_gate, top_expert, top_weight, row_gate, static_cast<int>(width), static_cast<int>(experts), \
+                           static_cast<int>(top), static_cast<int>(renormalize))
+    return hybrid::launched(HYB_DISPATCH(dtype, CALL), "moe_route_kernel");
+#undef CALL
+}
+
+int64_t hyb_moe_workspace_bytes(int64_t T, int64_t top, int64_t experts, int64_t width, int64_t ff, uint32_t dtype) {
+    if (T < 0 || top <= 0 || experts <= 0 || width <= 0 || ff <= 0) return -1;
+    return carve(std::max<int64_t>(T, 1), top, experts, width, ff, dtype, nullptr).total;
+}
+
+bool hyb_moe_experts(const atoma_moe_args &a, const void **expert_out, const int32_t **pair_row, cudaStream_t stream) {
+    if (a.T <= 0) return true;
+    if (!hybrid::known_dtype(a.dtype, "atoma_moe_experts")) return false;
+    if (!a.h || !a.top_expert || !a.top_weight || !a.w_gate_up || !a.w_down || !a.workspace || a.width <= 0 || a.ff <= 0 || a.top <= 0 ||
+        a.experts <= 0 || a.experts > kMaxExperts) {
+        set_status(kErrInvalidArg, "atoma_moe_experts: null argument or empty shape");
+        return false;
+    }
+    const MoeSpace s = carve(a.T, a.top, a.experts, a.width, a.ff, a.dtype, a.workspace);
+    if (s.total > a.workspace_bytes) {
+        set_status(kErrInvalidArg, "atoma_moe_experts: workspace of %lld bytes, %lld needed", static_cast<long long>(a.workspace_bytes),
+                   static_cast<long long>(s.total));
+        return false;
+    }
+    const int pairs = static_cast<int>(a.T * a.top);
+    if (!hybrid::launched(launch_ex(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, a.top_expert, s.pair_row, s.row_pair, s.tile_expert,
+                                    s.meta, pairs, static_cast<int>(a.experts), static_cast<int>(s.max_rows)),
+                          "moe_sort_kernel"))
+        return false;
+#define CALL(TT) launch_ex(moe_gather_kernel<TT>, dim3(static_cast<unsigned>(s.max_rows)), dim3(128), 0, stream, static_cast<const TT *>(a.h), \
+                           a.top_weight, static_cast<const int32_t *>(s.row_pair), static_cast<const int32_t *>(s.meta), \
+                           reinterpret_cast<TT *>(s.xs), static_cast<int>(a.width), static_cast<int>(a.top), static_cast<int>(a.scale_input))
+    if (!hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "moe_gather_kernel")) return false;
+#undef CALL
+    const float *no_weight = nullptr;
+    const dim3 g1(static_cast<unsigned>((a.ff + 63) / 64), static_cast<unsigned>(s.max_tiles));
+#define CALL(TT) launch_ex(moe_grouped_kernel<TT, true>, g1, dim3(256), 0, stream, reinterpret_cast<const TT *>(s.xs), \
+                           static_cast<const TT *>(a.w_gate_up), reinterpret_cast<TT *>(s.act), static_cast<const int32_t *>(s.tile_expert), \
+                           static_cast<const int32_t *>(s.meta), static_cast<const int32_t *>(s.row_pair), no_weight, \
+                           static_cast<int>(a.ff), static_cast<int>(a.width), a.limit, a.alpha, a.up_shift)
+    if (!hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "moe_grouped_kernel<glu>")) return false;
+#undef CALL
+    const float *ow = a.scale_input ? nullptr : a.top_weight;
+    const dim3 g2(static_cast<unsigned>((a.width + 63) / 64), static_cast<unsigned>(s.max_tiles));
+#define CALL(TT) launch_ex(moe_grouped_kernel<TT, false>, g2, dim3(256), 0, stream, reinterpret_cast<const TT *>(s.act), \
+                           static_cast<const TT *>(a.w_down), reinterpret_cast<TT *>(s.y), static_cast<const int32_t *>(s.tile_expert), \
+                           static_cast<const int32_t *>(s.meta), static_cast<const int32_t *>(s.row_pair), ow, static_cast<int>(a.width), \
+                           static_cast<int>(a.ff), 0.f, 0.f, 0.f)
+    if (!hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "moe_grouped_kernel<down>")) return false;
+#undef CALL
+    if (expert_out) *expert_out = s.y;
+    if (pair_row) *pair_row = s.pair_row;
+    return true;
+}
+
+}  // namespace atoma
+
+using namespace atoma;
+
+extern "C" void atoma_moe_route(const void *h, const float *w_router, const float *w_row_gate, int32_t *top_expert, float *top_weight,
+                                float *row_gate, int64_t T, int64_t width, int64_t experts, int64_t top, int32_t renormalize, uint32_t dtype,
+                                atoma_stream_t stream) {
+    clear_status();
+    hyb_moe_route(h, w_router, w_row_gate, top_expert, top_weight, row_gate, T, width, experts, top, renormalize, dtype,
+                  static_cast<cudaStream_t>(stream));
+}
+extern "C" int64_t atoma_moe_workspace_bytes(int64_t T, int64_t top, int64_t experts, int64_t width, int64_t ff, uint32_t dtype) {
+    return hyb_moe_workspace_bytes(T, top, experts, width, ff, dtype);
+}
+extern "C" void atoma_moe_experts(const atoma_moe_args *args, const void **expert_out, const int32_t **pair_row, atoma_stream_t stream) {
+    clear_status();
+    if (!args) {
+        set_status(kErrInvalidArg, "atoma_moe_experts: args is NULL");
+        return;
+    }
+    hyb_moe_experts(*args, expert_out, pair_row, static_cast<cudaStream_t>(stream));
+}

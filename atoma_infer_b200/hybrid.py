@@ -1,8 +1,10 @@
 """Hybrid (attention + recurrent) decoder models: description, device layout and the step executor's host side.
 
-A model family (atoma_infer_b200/lilovik.py is the first) describes itself as a `HybridSpec` — a list of
-layers, each a mixer (sigmoid attention or minGRU) with its sizes and constants and an optional gated
-feed-forward — and hands over its weights under the generic names below.  `HybridExecutor` lays them out
+A model family (atoma_infer_b200/lilovik.py is the first, patadra.py the second) describes itself as a
+`HybridSpec` — a list of layer RUNS, each a mixer (sigmoid attention, minGRU or latent attention) with its
+sizes and constants and an optional feed-forward (gated dense, or a mixture of experts) — and hands over its
+weights under the generic names below.  A design that runs a span of layers several times lists every run;
+runs that name the same `source` share one copy of the weights and have caches of their own.  `HybridExecutor` lays them out
 on the device, owns the paged key/value caches and the recurrent-state slots, and runs one step of a MIXED
 batch (portions of prompts beside single decoded tokens) through ONE C call, `atoma_hybrid_step`
 (csrc/hybrid_step.cu).  The step's integer inputs are built by the same `atoma_prepare_input` /
@@ -14,6 +16,11 @@ Weight layout (rows stacked so that one GEMM makes all projections of a sublayer
   w_gate_up [2 ff, width]                     w_down  [width, ff]
   w_o       [width, H vdim] or [width, S]
   norms, q/k norm weights, talking-heads matrix, per-head bias and distance slopes: float32.
+Pre-norm designs (block_style "prenorm"):
+  w_down_in [q_rank + kv_rank (+ width), width]   query latent, key/value latent, residual gate rows
+  w_uq [H dim, q_rank]   w_uk [H dim, kv_rank]   w_uv [H vdim, kv_rank]   dq_norm, dkv_norm, sink, gate biases: float32
+  w_ff_in [2 shared_ff (+ width), width]   w_down [width, shared_ff]   w_router [experts, width] float32
+  w_expert_gate_up [experts, 2 ff, width]   w_expert_down [experts, width, ff]   side_gate, side_proj, side_norm
 """
 from __future__ import annotations
 
@@ -31,7 +38,8 @@ from .ops import AtomaError
 from .scheduler import StepPlan
 from .worker import InputStager, SequenceInput
 
-MIXER_ATTENTION, MIXER_MINGRU = 0, 1
+MIXER_ATTENTION, MIXER_MINGRU, MIXER_LATENT = 0, 1, 2
+BLOCK_STYLES = {"sandwich": 0, "prenorm": 1}
 ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
 DTYPE_CODES = {torch.bfloat16: 1, torch.float32: 2}
 
@@ -61,11 +69,44 @@ class MlpSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Queries, keys and values expanded from low-rank latents; the key/value latent alone is cached."""
+    heads: int
+    dim: int
+    vdim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    window: int = 0                # 0 = every earlier token is visible
+    sink: bool = False             # a learned per-head term of the softmax denominator
+
+
+@dataclass(frozen=True)
+class MoeSpec:
+    """Sigmoid-routed experts with a clamped gated activation g sigmoid(alpha g) (u + up_shift), and an optional shared expert."""
+    experts: int
+    top: int
+    ff: int
+    limit: float = 0.0             # clamp of gate (above) and up (both sides); 0 = none
+    shared_ff: int = 0             # 0 = no shared expert
+    shared_limit: float = 0.0
+    shared_gate: bool = False      # the shared expert's output times sigmoid(w . h)
+    alpha: float = 1.702
+    up_shift: float = 1.0
+    renormalize: bool = False      # chosen scores divided by their sum
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    mixer: str                               # "attention" | "mingru"
+    mixer: str                               # "attention" | "mingru" | "latent_attention"
     attention: Optional[AttentionSpec] = None
     mingru: Optional[MinGruSpec] = None
     mlp: Optional[MlpSpec] = None
+    latent: Optional[LatentAttentionSpec] = None
+    moe: Optional[MoeSpec] = None
+    gated_residual: bool = False             # sublayer results times sigmoid(W h + b) before they join the stream
+    side_part: Optional[int] = None          # which part of the token side table the layer reads; None = no side input
+    source: Optional[int] = None             # entry of weights["layers"] the run uses; None = its own index
 
 
 @dataclass(frozen=True)
@@ -77,6 +118,12 @@ class HybridSpec:
     layers: Seq_[LayerSpec] = ()
     norm_offset: float = 1.0                 # norm weights are stored as offsets from this value
     position_base: float = 10000.0
+    block_style: str = "sandwich"            # "sandwich": x += norm(f(norm x));  "prenorm": x += gate * f(norm x)
+    norm_groups: int = 1                     # RMS statistics over this many equal consecutive parts of the row
+    position: str = "sinusoid"               # "sinusoid" | "learned" (a table of max_positions rows)
+    max_positions: int = 0
+    logit_softcap: float = 0.0               # logits <- cap * tanh(logits / cap); 0 = none
+    side_dim: int = 0                        # width of one layer's part of the token side table
 
     @property
     def has_state(self) -> bool:
@@ -84,7 +131,8 @@ class HybridSpec:
 
     def cache_bytes_per_token(self, dtype: torch.dtype) -> int:
         es = torch.empty((), dtype=dtype).element_size()
-        return sum(l.attention.kv_heads * (l.attention.dim + l.attention.vdim) * es for l in self.layers if l.mixer == "attention")
+        return (sum(l.attention.kv_heads * (l.attention.dim + l.attention.vdim) * es for l in self.layers if l.mixer == "attention") +
+                sum(l.latent.kv_rank * es for l in self.layers if l.mixer == "latent_attention"))
 
 
 @dataclass
@@ -119,18 +167,46 @@ class HybridExecutor:
             self._keep.append(t)
             return t
 
+        if spec.block_style not in BLOCK_STYLES:
+            raise AtomaError(f"unknown block style {spec.block_style!r}")
         self.embed, self.head = big(weights["embed"]), big(weights["head"])
         self.final_norm = small(weights["final_norm"])
-        half = (spec.width + 1) // 2
-        inv = np.array([spec.position_base ** (-2.0 * i / spec.width) for i in range(half)], dtype=np.float64)
-        self.inv_freq = torch.from_numpy(inv).to(dev)
+        self.inv_freq = self.pos_table = self.side_table = None
+        if spec.position == "learned":
+            self.pos_table = big(weights["pos"])
+            if self.pos_table.shape[0] < spec.max_positions or spec.max_positions <= 0:
+                raise AtomaError(f"position table of {self.pos_table.shape[0]} rows for {spec.max_positions} positions")
+        else:
+            half = (spec.width + 1) // 2
+            inv = np.array([spec.position_base ** (-2.0 * i / spec.width) for i in range(half)], dtype=np.float64)
+            self.inv_freq = torch.from_numpy(inv).to(dev)
+        if spec.side_dim > 0:
+            self.side_table = big(weights["side_table"])
         self.k_caches: List[Optional[torch.Tensor]] = []
         self.v_caches: List[Optional[torch.Tensor]] = []
+        self.latent_caches: List[Optional[torch.Tensor]] = []
         self.states: List[Optional[torch.Tensor]] = []
         self._layers = (HybridLayer * len(spec.layers))()
         rows = self.num_blocks * self.block_size
-        for i, (ls, w) in enumerate(zip(spec.layers, weights["layers"])):
+        placed: Dict[int, HybridLayer] = {}      # weights already on the device, by their entry of weights["layers"]
+        for i, ls in enumerate(spec.layers):
             L = self._layers[i]
+            src = i if ls.source is None else ls.source
+            w = weights["layers"][src]
+            if spec.block_style == "prenorm":
+                if src in placed:
+                    C.memmove(C.byref(L), C.byref(placed[src]), C.sizeof(HybridLayer))     # same weights, a cache of its own below
+                else:
+                    self._place_prenorm(L, i, ls, w, big, small)
+                    placed[src] = L
+                lc = torch.zeros((rows, ls.latent.kv_rank), dtype=dtype, device=dev)
+                L.latent_cache = lc.data_ptr()
+                self.k_caches.append(None)
+                self.v_caches.append(None)
+                self.states.append(None)
+                self.latent_caches.append(lc)
+                continue
+            self.latent_caches.append(None)
             L.norm1, L.norm1b = small(w["norm1"]).data_ptr(), small(w["norm1b"]).data_ptr()
             L.has_mlp = 1 if ls.mlp is not None else 0
             kc = vc = st = None
@@ -170,9 +246,15 @@ class HybridExecutor:
         m = HybridModel()
         m.width, m.vocab, m.num_layers, m.block_size = spec.width, spec.vocab, len(spec.layers), self.block_size
         m.eps, m.logit_scale, m.norm_offset, m.dtype = spec.eps, spec.logit_scale, spec.norm_offset, DTYPE_CODES[dtype]
-        m.embed, m.inv_freq = self.embed.data_ptr(), self.inv_freq.data_ptr()
+        m.embed = self.embed.data_ptr()
+        m.inv_freq = self.inv_freq.data_ptr() if self.inv_freq is not None else None
         m.final_norm, m.head = self.final_norm.data_ptr(), self.head.data_ptr()
         m.layers = C.cast(self._layers, C.POINTER(HybridLayer))
+        m.block_style, m.norm_groups = BLOCK_STYLES[spec.block_style], spec.norm_groups
+        m.pos_table = self.pos_table.data_ptr() if self.pos_table is not None else None
+        m.max_positions, m.logit_softcap = spec.max_positions, spec.logit_softcap
+        if self.side_table is not None:
+            m.side_table, m.side_dim, m.side_table_width = self.side_table.data_ptr(), spec.side_dim, self.side_table.shape[1]
         self._model = m
         self._stager = InputStager(device=dev, block_size=self.block_size, enable_chunked_prefill=True)
         self._extra_host = None
@@ -181,6 +263,46 @@ class HybridExecutor:
         self._logits = None
         self._next = None
         self.launches_last_step = 0
+
+    def _place_prenorm(self, L, i: int, ls: LayerSpec, w: dict, big, small) -> None:
+        """Device copies and sizes of one pre-norm layer (latent attention, optional experts, optional side input)."""
+        if ls.mixer != "latent_attention" or ls.latent is None:
+            raise AtomaError(f"layer {i}: pre-norm blocks take the latent-attention mixer, not {ls.mixer!r}")
+        a = ls.latent
+        L.mixer = MIXER_LATENT
+        L.heads, L.kv_heads, L.dim, L.vdim = a.heads, 1, a.dim, a.vdim
+        L.q_rank, L.kv_rank, L.window, L.scale = a.q_rank, a.kv_rank, a.window, a.scale
+        L.norm1 = small(w["norm1"]).data_ptr()
+        L.w_down_in = big(w["w_down_in"]).data_ptr()
+        L.dq_norm, L.dkv_norm = small(w["dq_norm"]).data_ptr(), small(w["dkv_norm"]).data_ptr()
+        L.sink = small(w["sink"]).data_ptr() if a.sink else None
+        L.w_uq, L.w_uk, L.w_uv, L.w_o = (big(w[k]).data_ptr() for k in ("w_uq", "w_uk", "w_uv", "w_o"))
+        L.gate1_bias = small(w["gate1_bias"]).data_ptr() if ls.gated_residual else None
+        has_ff = ls.moe is not None or ls.mlp is not None
+        L.has_mlp = 1 if has_ff else 0
+        if has_ff:
+            L.norm2 = small(w["norm2"]).data_ptr()
+            L.gate2_bias = small(w["gate2_bias"]).data_ptr() if ls.gated_residual else None
+        if ls.moe is not None:
+            e = ls.moe
+            if not 0 < e.top <= e.experts:
+                raise AtomaError(f"layer {i}: top {e.top} of {e.experts} experts")
+            L.ff_kind, L.renormalize = 1, 1 if e.renormalize else 0
+            L.experts, L.top, L.expert_ff, L.ff = e.experts, e.top, e.ff, e.shared_ff
+            L.expert_limit, L.shared_limit, L.act_alpha, L.act_up_shift = e.limit, e.shared_limit, e.alpha, e.up_shift
+            L.w_router = small(w["w_router"]).data_ptr()
+            L.w_expert_gate_up, L.w_expert_down = big(w["w_expert_gate_up"]).data_ptr(), big(w["w_expert_down"]).data_ptr()
+            if e.shared_ff > 0:
+                L.w_down = big(w["w_down"]).data_ptr()
+                L.w_shared_gate = small(w["w_shared_gate"]).data_ptr() if e.shared_gate else None
+            if e.shared_ff > 0 or ls.gated_residual:
+                L.w_ff_in = big(w["w_ff_in"]).data_ptr()
+        elif ls.mlp is not None:
+            raise AtomaError(f"layer {i}: pre-norm blocks have a mixture-of-experts feed-forward or none")
+        if ls.side_part is not None:
+            L.side_part = ls.side_part
+            L.side_gate, L.side_proj = big(w["side_gate"]).data_ptr(), big(w["side_proj"]).data_ptr()
+            L.side_norm = small(w["side_norm"]).data_ptr()
 
     # ---- buffers (grow-only) ----
     def _reserve(self, T: int, S: int) -> None:
@@ -220,6 +342,8 @@ class HybridExecutor:
         t0 = 0
         for b, c in enumerate(chunks):
             end = c.start + c.count
+            if self.spec.max_positions and end > self.spec.max_positions:
+                raise AtomaError(f"sequence {c.seq.seq_id}: {end} tokens, the model has {self.spec.max_positions} positions")
             if -(-end // self.block_size) > len(c.block_table):
                 raise AtomaError(f"sequence {c.seq.seq_id}: {end} tokens need more pages than its block table holds")
             ids = np.zeros(end, dtype=np.uint32)            # only the chunk's tokens are read (positions start .. end)

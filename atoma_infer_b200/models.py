@@ -63,10 +63,19 @@ def _lilovik_needs_state(cfg) -> bool:
     return any(l["type"] == "mingru" for l in cfg["layers"])
 
 
+def _build_patadra(cfg, ckpt, dtype, device, cache: CacheConfig):
+    from . import patadra
+    from .hybrid import HybridExecutor
+    spec = patadra.spec_from_config(cfg)
+    weights = patadra.weights_from_checkpoint(spec, cfg, ckpt)
+    return HybridExecutor(spec, weights, dtype, device, cache.num_blocks, cache.block_size, cache.num_state_slots)
+
+
 def _build_llama(cfg, ckpt, dtype, device, cache: CacheConfig):
     from .llama_engine import LlamaExecutor
     return LlamaExecutor.from_checkpoint(cfg, ckpt, dtype, device, cache)
 
 
 register_model("Lilovik", _build_lilovik, _lilovik_needs_state)
+register_model("Patadra", _build_patadra)
 register_model("LlamaForCausalLM", _build_llama)

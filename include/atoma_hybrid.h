@@ -10,6 +10,15 @@
  * feed-forward.  Every constant of those mechanisms is an argument, so that another design can use
  * the operator with other values.
  *
+ * The second design is Patadra: a learned position table, pre-norm layers with RMS norms taken over
+ * equal consecutive groups of the row, sublayer results gated by a sigmoid of a projection of the
+ * sublayer's input before they join the residual stream, latent attention (queries, keys and values
+ * expanded from low-rank latents; only the key/value latent is cached) under a sliding window with a
+ * per-head softmax sink, a mixture-of-experts feed-forward with a sigmoid router whose score scales the
+ * expert's INPUT, a clamped gated activation, an always-on shared expert, a per-layer token input
+ * looked up in a side table, and a tanh cap on the logits.  A span of layers may run several times
+ * with the same weights; every run is one entry of the layer list with a cache of its own.
+ *
  * Conventions: row-major; `dtype` is the number format of activations, large weights and the caches:
  * 1 = bfloat16, 2 = float32 (true 32-bit arithmetic: no reduced-precision matrix mode).  Whatever the
  * dtype, the residual stream, norm statistics, attention scores and weights, recurrent state and all
@@ -103,9 +112,144 @@ void atoma_scale_logits_greedy(const void *logits, float *logits_f32, uint32_t *
                                float scale, uint32_t dtype, atoma_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------ */
+/* Pre-norm designs with gated residuals, latent attention and mixtures of experts             */
+/* ------------------------------------------------------------------------------------------ */
+
+/* out[t, :] = table[tokens[t], :] + pos_table[positions[t], :] (float32 sum; positions beyond max_positions - 1 are an
+ * error the caller must exclude: the kernel clamps). */
+void atoma_embed_learned(const uint32_t *tokens, const int64_t *positions, const void *table, const void *pos_table, float *out,
+                         int64_t T, int64_t width, int64_t vocab, int64_t max_positions, uint32_t dtype, atoma_stream_t stream);
+
+/* RMS norm in `groups` equal consecutive parts of the row, each divided by its own sqrt(mean(part^2) + eps); the whole
+ * row is then multiplied by (weight_offset + weight).  groups = 1 is atoma_rmsnorm_rows.  width % groups == 0. */
+void atoma_group_rmsnorm_rows(const float *x, const int32_t *rows, const float *weight, float weight_offset, int64_t groups,
+                              void *out, int64_t R, int64_t width, float eps, uint32_t dtype, atoma_stream_t stream);
+
+/*
+ * Residual update of a pre-norm layer and the next sublayer's input norm in ONE kernel.  Per token t and channel c:
+ *   v = (y ? y[t, c] * (row_scale ? row_scale[t] : 1) : 0) + sum_{k < top} expert_out[pair_row[t top + k], c]
+ *   x[t, c] += gate ? v * sigmoid(gate[t, c] + gate_bias[c]) : v
+ *   h[t, :]  = group_rmsnorm(x[t, :]) * (weight_offset + w_next)      (w_next NULL: no norm)
+ *   x_cast[t, :] = x[t, :] in `dtype`                                  (x_cast NULL: not written)
+ * y, gate, expert_out, h, x_cast in `dtype` with row strides ld_y, ld_gate, width, width, width; x float32 in place.
+ * The experts' rows are added in the order k = 0 .. top - 1.
+ */
+typedef struct atoma_gated_residual_args {
+    const void *y;
+    int64_t ld_y;
+    const float *row_scale;       /* [T] or NULL */
+    const void *expert_out;       /* [rows, width] or NULL */
+    const int32_t *pair_row;      /* [T top] row of expert_out that holds pair (t, k) */
+    int64_t top;
+    const void *gate;             /* pre-activation of the residual gate, or NULL */
+    int64_t ld_gate;
+    const float *gate_bias;       /* [width] */
+    float *x;                     /* [T, width] */
+    const float *w_next;          /* [width] or NULL */
+    void *h;                      /* [T, width] */
+    void *x_cast;                 /* [T, width] or NULL */
+    int64_t T, width, groups;
+    float eps, weight_offset;
+    uint32_t dtype;
+} atoma_gated_residual_args;
+void atoma_gated_residual_norm(const atoma_gated_residual_args *args, atoma_stream_t stream);
+
+/* Token side input, gate part: out[t, j] = gelu_tanh(a[t, j]) * side_table[tokens[t], part * dim + j], j < dim.
+ * a (row stride ld_a) and out [T, dim] in `dtype`; side_table [vocab, table_width] in `dtype`. */
+void atoma_side_gate(const void *a, int64_t ld_a, const uint32_t *tokens, const void *side_table, int64_t table_width, int64_t part,
+                     void *out, int64_t T, int64_t dim, int64_t vocab, uint32_t dtype, atoma_stream_t stream);
+
+/* x[t, :] += y[t, :] / sqrt(mean(y^2) + eps) * w_unit;  h[t, :] = group_rmsnorm(x[t, :]) * (weight_offset + w_next) (NULL: none). */
+void atoma_unitnorm_add_norm(const void *y, float *x, const float *w_unit, const float *w_next, void *h, int64_t T, int64_t width,
+                             int64_t groups, float eps, float weight_offset, uint32_t dtype, atoma_stream_t stream);
+
+/* After the fused down projections proj[t, :] = [c_q (q_rank) | c (kv_rank) | ...] (row stride ld):
+ *   cq_out[t, :] = rms(c_q) * q_weight  (q_rank = 0: no query latent)      latent_cache[slot_mapping[t], :] = rms(c) * kv_weight
+ * plain weights; cq_out and the cache [num_blocks * block_size, kv_rank] in `dtype`; slot < 0 is skipped. */
+void atoma_latent_norm_cache(const void *proj, int64_t ld, const float *q_weight, const float *kv_weight, const int64_t *slot_mapping,
+                             void *cq_out, void *latent_cache, int64_t T, int64_t q_rank, int64_t kv_rank, float eps, uint32_t dtype,
+                             atoma_stream_t stream);
+
+/* Per-head projection between a head's own space and a shared latent, w [H n, R] (stored [out, in], as the checkpoint has it):
+ *   absorb = 1:  out[t, h, r] = sum_j in[t, h n + j] w[h n + j, r]     in [T, H n] `dtype`      -> out [T, H, R] float32
+ *   absorb = 0:  out[t, h n + j] = sum_r in[t, h, r] w[h n + j, r]     in [T, H, R] float32    -> out [T, H n] `dtype`
+ * The first moves a query into the latent space of the keys (so that q . (W c) = (W^T q) . c needs no expanded keys);
+ * the second expands a head's weighted sum of latents into its values. */
+void atoma_head_project(const void *in, const void *w, void *out, int64_t T, int64_t H, int64_t n, int64_t R, int32_t absorb,
+                        uint32_t dtype, atoma_stream_t stream);
+
+/*
+ * Softmax attention of H heads over ONE shared cached latent per token (keys = values = the latent), paged, mixed batch.
+ * For query token t of sequence b at position p and keys j with 0 <= p - j < window (window <= 0: every j <= p):
+ *   s_h(j) = (q_lat[t, h, :] . c_j) * scale
+ *   w_h(j) = exp(s_h(j)) / (sum_j' exp(s_h(j')) + (sink ? exp(sink[h]) : 0))
+ *   out[t, h, :] = sum_j w_h(j) c_j
+ * q_lat and out float32 [T, H, R]; scores, weights and sums float32.
+ */
+typedef struct atoma_latent_attn_args {
+    const float *q_lat;
+    const void *latent_cache;     /* [num_blocks * block_size, R] `dtype` */
+    float *out;
+    const int64_t *positions;     /* [T] */
+    const int32_t *token_seq;     /* [T] */
+    const int32_t *query_start;   /* [B + 1] */
+    const int32_t *block_tables;  /* [B, max_blocks] */
+    const float *sink;            /* [H] or NULL */
+    int64_t T, B, max_blocks, H, R, block_size, window;
+    float scale;
+    uint32_t dtype;
+    int32_t max_query_len, max_seq_len;
+} atoma_latent_attn_args;
+void atoma_latent_attention_paged(const atoma_latent_attn_args *args, atoma_stream_t stream);
+
+/* Router of a mixture of experts, float32: z = w_router h (h [T, width] `dtype`, w_router [experts, width] float32),
+ * s = sigmoid(z) (score_fn 0) ; the `top` largest scores (ties: the lower index) -> top_expert [T, top] int32 and
+ * top_weight [T, top] float32 = the chosen scores as they are (renormalize 0) or divided by their sum (1).
+ * w_row_gate (float32 [width], may be NULL): row_gate[t] = sigmoid(w_row_gate . h[t]) — the shared expert's gate. */
+void atoma_moe_route(const void *h, const float *w_router, const float *w_row_gate, int32_t *top_expert, float *top_weight,
+                     float *row_gate, int64_t T, int64_t width, int64_t experts, int64_t top, int32_t renormalize, uint32_t dtype,
+                     atoma_stream_t stream);
+
+/* y = act(g, u) of a gated feed-forward with clamps: g = min(gu[t, j], limit), u = clamp(gu[t, ff + j], -limit, limit),
+ * out[t, j] = g * sigmoid(alpha g) * (u + up_shift).  limit <= 0: no clamp.  gu row stride ld. */
+void atoma_glu_clamped(const void *gu, int64_t ld, void *out, int64_t T, int64_t ff, float limit, float alpha, float up_shift,
+                       uint32_t dtype, atoma_stream_t stream);
+
+/*
+ * The routed experts of a step: every (token, k) pair is sorted by its expert on the device (no host read), its input row
+ * h[t] * top_weight[t, k] is gathered (scale_input 1; with 0 the weight multiplies the expert's output instead), and the
+ * experts run as two grouped products with the clamped gated activation between them:
+ *   expert_out[pair_row[t top + k], :] = w_down[e] act(w_gate_up[e] (weight * h[t]))
+ * w_gate_up [experts, 2 ff, width] (gate rows, then up rows), w_down [experts, width, ff], all `dtype`.
+ * workspace: atoma_moe_workspace_bytes(T, top, experts, width, ff, dtype) bytes; expert_out and pair_row point into it
+ * and are returned through *expert_out / *pair_row for atoma_gated_residual_norm.
+ */
+typedef struct atoma_moe_args {
+    const void *h;                /* [T, width] */
+    const int32_t *top_expert;    /* [T, top] */
+    const float *top_weight;      /* [T, top] */
+    const void *w_gate_up, *w_down;
+    void *workspace;
+    int64_t workspace_bytes;
+    int64_t T, width, experts, top, ff;
+    float limit, alpha, up_shift;
+    int32_t scale_input;
+    uint32_t dtype;
+} atoma_moe_args;
+int64_t atoma_moe_workspace_bytes(int64_t T, int64_t top, int64_t experts, int64_t width, int64_t ff, uint32_t dtype);
+void atoma_moe_experts(const atoma_moe_args *args, const void **expert_out, const int32_t **pair_row, atoma_stream_t stream);
+
+/* logits_f32[r, :] = cap(logits[r, :] * scale), cap(v) = softcap * tanh(v / softcap) (softcap <= 0: identity), and
+ * token_out[r] = the last index of the row's maximum. */
+void atoma_finish_logits_greedy(const void *logits, float *logits_f32, uint32_t *token_out, int64_t R, int64_t vocab, float scale,
+                                float softcap, uint32_t dtype, atoma_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------ */
 /* Step executor                                                                                */
 /* ------------------------------------------------------------------------------------------ */
-enum { ATOMA_MIXER_SIGMOID_ATTENTION = 0, ATOMA_MIXER_MINGRU = 1 };
+enum { ATOMA_MIXER_SIGMOID_ATTENTION = 0, ATOMA_MIXER_MINGRU = 1, ATOMA_MIXER_LATENT_ATTENTION = 2 };
+enum { ATOMA_BLOCK_SANDWICH = 0, ATOMA_BLOCK_PRENORM = 1 };
+enum { ATOMA_FF_DENSE = 0, ATOMA_FF_MOE = 1 };
 enum { ATOMA_ACT_SILU = 0, ATOMA_ACT_RELU = 1, ATOMA_ACT_GELU_TANH = 2 };
 
 typedef struct atoma_hybrid_layer {
@@ -130,6 +274,27 @@ typedef struct atoma_hybrid_layer {
     int32_t act;
     const void *w_gate_up;  /* [2 ff, width] */
     const void *w_down;     /* [width, ff] */
+    /* ---- pre-norm blocks (model.block_style = ATOMA_BLOCK_PRENORM) ---- */
+    /* latent attention (uses heads, dim, vdim, scale above) */
+    int64_t q_rank, kv_rank, window;   /* window <= 0: every earlier token is visible */
+    const void *w_down_in;  /* [q_rank + kv_rank (+ width with a gated residual), width]: query latent, key/value latent, residual gate */
+    const float *dq_norm, *dkv_norm, *sink;
+    const void *w_uq, *w_uk, *w_uv;    /* [H dim, q_rank], [H dim, kv_rank], [H vdim, kv_rank] */
+    void *latent_cache;     /* [num_blocks * block_size, kv_rank] */
+    /* gated residuals: bias of the gate, NULL = the sublayer's result is added as it is */
+    const float *gate1_bias, *gate2_bias;
+    /* mixture of experts (ff_kind = ATOMA_FF_MOE): ff above = the shared expert's size (0: none) */
+    int32_t ff_kind, renormalize;
+    int64_t experts, top, expert_ff;
+    float expert_limit, shared_limit, act_alpha, act_up_shift;
+    const float *w_router;  /* [experts, width] float32 */
+    const float *w_shared_gate; /* [width] float32 or NULL */
+    const void *w_expert_gate_up, *w_expert_down;
+    const void *w_ff_in;    /* [2 ff (+ width with a gated residual), width]: shared gate rows, up rows, residual gate */
+    /* token side input after the feed-forward (side_gate NULL: none) */
+    int64_t side_part;
+    const void *side_gate, *side_proj; /* [side_dim, width], [width, side_dim] */
+    const float *side_norm;
 } atoma_hybrid_layer;
 
 typedef struct atoma_hybrid_model {
@@ -141,6 +306,14 @@ typedef struct atoma_hybrid_model {
     const float *final_norm;
     const void *head;       /* [vocab, width] */
     const atoma_hybrid_layer *layers; /* host array */
+    /* ---- pre-norm designs ---- */
+    int32_t block_style;    /* ATOMA_BLOCK_* */
+    int32_t norm_groups;    /* 0 or 1: whole-row norms */
+    const void *pos_table;  /* [max_positions, width] learned positions (then inv_freq may be NULL) */
+    int64_t max_positions;
+    float logit_softcap;    /* <= 0: none */
+    const void *side_table; /* [vocab, side_table_width] */
+    int64_t side_dim, side_table_width;
 } atoma_hybrid_model;
 
 typedef struct atoma_hybrid_batch {
@@ -162,7 +335,7 @@ typedef struct atoma_hybrid_batch {
     float *residual_trace;        /* optional out [num_layers, T, width]: the residual stream after every layer */
 } atoma_hybrid_batch;
 
-int64_t atoma_hybrid_abi_sizeof(int which); /* 0 layer, 1 model, 2 batch, 3 attention args */
+int64_t atoma_hybrid_abi_sizeof(int which); /* 0 layer, 1 model, 2 batch, 3 attention args, 4 gated residual args, 5 latent attention args, 6 expert args */
 int64_t atoma_hybrid_scratch_bytes(const atoma_hybrid_model *model, int64_t num_tokens, int64_t num_selected);
 void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_hybrid_batch *batch, atoma_stream_t stream);
 
