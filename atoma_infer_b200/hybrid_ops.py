@@ -131,3 +131,153 @@ def gate_up_act(x, w_gate_up, act: int):
     _lib.lib().atoma_gate_up_act(_p(x), _p(w_gate_up), _p(out), T, ff, x.shape[1], x.shape[1], x.shape[1], ff, act, 1, _s())
     _check()
     return out
+
+
+# ---- pre-norm designs: learned positions, grouped norms, gated residuals, latent attention, mixtures of experts ----
+def embed_learned(tokens, positions, table, pos_table):
+    T, W = tokens.numel(), table.shape[1]
+    out = torch.empty((T, W), dtype=torch.float32, device=table.device)
+    _lib.lib().atoma_embed_learned(_p(tokens), _p(positions), _p(table), _p(pos_table), _p(out), T, W, table.shape[0], pos_table.shape[0],
+                                   _CODES[table.dtype], _s())
+    _check()
+    return out
+
+
+def group_rmsnorm_rows(x, weight, offset, groups, eps, dtype, rows=None):
+    R = x.shape[0] if rows is None else rows.numel()
+    out = torch.empty((R, x.shape[1]), dtype=dtype, device=x.device)
+    _lib.lib().atoma_group_rmsnorm_rows(_p(x), _p(rows), _p(weight), offset, groups, _p(out), R, x.shape[1], eps, _CODES[dtype], _s())
+    _check()
+    return out
+
+
+def gated_residual_norm(x, y=None, gate=None, gate_bias=None, row_scale=None, expert_out=None, pair_row=None, top=0, w_next=None,
+                        groups=1, eps=1e-5, offset=0.0, want_cast=False):
+    """x (float32) is updated in place; returns (h, x_cast), each None when not asked for.  y / gate may be column slices of a
+    wider row-major matrix (their row stride is passed on)."""
+    from ._lib import GatedResidualArgs
+    ref = y if y is not None else expert_out
+    T, W = x.shape
+    h = torch.empty((T, W), dtype=ref.dtype, device=x.device) if w_next is not None else None
+    xc = torch.empty((T, W), dtype=ref.dtype, device=x.device) if want_cast else None
+    a = GatedResidualArgs()
+    a.y, a.ld_y = _p(y), (y.stride(0) if y is not None else 0)
+    a.row_scale, a.expert_out, a.pair_row, a.top = _p(row_scale), _p(expert_out), _p(pair_row), top
+    a.gate, a.ld_gate, a.gate_bias = _p(gate), (gate.stride(0) if gate is not None else 0), _p(gate_bias)
+    a.x, a.w_next, a.h, a.x_cast = _p(x), _p(w_next), _p(h), _p(xc)
+    a.T, a.width, a.groups, a.eps, a.weight_offset, a.dtype = T, W, groups, eps, offset, _CODES[ref.dtype]
+    _lib.lib().atoma_gated_residual_norm(C.byref(a), _s())
+    _check()
+    return h, xc
+
+
+def side_gate(a, tokens, side_table, part, dim):
+    T = a.shape[0]
+    out = torch.empty((T, dim), dtype=a.dtype, device=a.device)
+    _lib.lib().atoma_side_gate(_p(a), a.stride(0), _p(tokens), _p(side_table), side_table.shape[1], part, _p(out), T, dim,
+                               side_table.shape[0], _CODES[a.dtype], _s())
+    _check()
+    return out
+
+
+def unitnorm_add_norm(y, x, w_unit, w_next, groups, eps, offset=0.0):
+    h = torch.empty_like(y) if w_next is not None else None
+    _lib.lib().atoma_unitnorm_add_norm(_p(y), _p(x), _p(w_unit), _p(w_next), _p(h), y.shape[0], y.shape[1], groups, eps, offset,
+                                       _CODES[y.dtype], _s())
+    _check()
+    return h
+
+
+def latent_norm_cache(proj, q_weight, kv_weight, slots, cache, q_rank, kv_rank, eps):
+    T = proj.shape[0]
+    cq = torch.empty((T, q_rank), dtype=proj.dtype, device=proj.device) if q_rank > 0 else None
+    _lib.lib().atoma_latent_norm_cache(_p(proj), proj.stride(0), _p(q_weight), _p(kv_weight), _p(slots), _p(cq), _p(cache), T, q_rank,
+                                       kv_rank, eps, _CODES[proj.dtype], _s())
+    _check()
+    return cq
+
+
+def head_project(x, w, H, n, R, absorb: bool):
+    """absorb: x [T, H n] -> float32 [T, H, R];  else x float32 [T, H, R] -> [T, H n] in w's format."""
+    T = x.shape[0]
+    out = (torch.empty((T, H, R), dtype=torch.float32, device=x.device) if absorb
+           else torch.empty((T, H * n), dtype=w.dtype, device=x.device))
+    _lib.lib().atoma_head_project(_p(x), _p(w), _p(out), T, H, n, R, 1 if absorb else 0, _CODES[w.dtype], _s())
+    _check()
+    return out
+
+
+def latent_attention_paged(q_lat, cache, positions, token_seq, block_tables, sink, H, R, block_size, window, scale, max_query_len,
+                           query_start=None, max_seq_len=None):
+    from ._lib import LatentAttnArgs
+    T = q_lat.shape[0]
+    if query_start is None:
+        counts = torch.bincount(token_seq.long(), minlength=block_tables.shape[0])
+        query_start = torch.cat([counts.new_zeros(1), counts.cumsum(0)]).to(torch.int32)
+    if max_seq_len is None:
+        max_seq_len = int(positions.max()) + 1
+    out = torch.empty((T, H, R), dtype=torch.float32, device=q_lat.device)
+    a = LatentAttnArgs()
+    a.q_lat, a.latent_cache, a.out = _p(q_lat), _p(cache), _p(out)
+    a.positions, a.token_seq, a.query_start, a.block_tables, a.sink = _p(positions), _p(token_seq), _p(query_start), _p(block_tables), _p(sink)
+    a.T, a.B, a.max_blocks, a.H, a.R, a.block_size, a.window = T, block_tables.shape[0], block_tables.shape[1], H, R, block_size, window
+    a.scale, a.dtype, a.max_query_len, a.max_seq_len = scale, _CODES[cache.dtype], max_query_len, int(max_seq_len)
+    _lib.lib().atoma_latent_attention_paged(C.byref(a), _s())
+    _check()
+    return out
+
+
+def moe_route(h, w_router, w_row_gate, top, renormalize=False):
+    T, E = h.shape[0], w_router.shape[0]
+    idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
+    wgt = torch.empty((T, top), dtype=torch.float32, device=h.device)
+    rg = torch.empty((T,), dtype=torch.float32, device=h.device) if w_row_gate is not None else None
+    _lib.lib().atoma_moe_route(_p(h), _p(w_router), _p(w_row_gate), _p(idx), _p(wgt), _p(rg), T, h.shape[1], E, top,
+                               1 if renormalize else 0, _CODES[h.dtype], _s())
+    _check()
+    return idx, wgt, rg
+
+
+def glu_clamped(gu, ff, limit, alpha, up_shift):
+    T = gu.shape[0]
+    out = torch.empty((T, ff), dtype=gu.dtype, device=gu.device)
+    _lib.lib().atoma_glu_clamped(_p(gu), gu.stride(0), _p(out), T, ff, limit, alpha, up_shift, _CODES[gu.dtype], _s())
+    _check()
+    return out
+
+
+def moe_experts(h, top_expert, top_weight, w_gate_up, w_down, limit, alpha, up_shift, scale_input=True):
+    """Returns the token's summed expert outputs as float32 [T, width] (the rows are summed here on the host side of the call
+    for tests; the step executor sums them inside its residual kernel)."""
+    from ._lib import MoeArgs
+    T, W = h.shape
+    E, ff2, _ = w_gate_up.shape
+    top = top_expert.shape[1]
+    code = _CODES[h.dtype]
+    nbytes = int(_lib.lib().atoma_moe_workspace_bytes(T, top, E, W, ff2 // 2, code))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=h.device)
+    a = MoeArgs()
+    a.h, a.top_expert, a.top_weight, a.w_gate_up, a.w_down = _p(h), _p(top_expert), _p(top_weight), _p(w_gate_up), _p(w_down)
+    a.workspace, a.workspace_bytes = _p(ws), nbytes
+    a.T, a.width, a.experts, a.top, a.ff = T, W, E, top, ff2 // 2
+    a.limit, a.alpha, a.up_shift, a.scale_input, a.dtype = limit, alpha, up_shift, 1 if scale_input else 0, code
+    eo, pr = C.c_void_p(), C.c_void_p()
+    _lib.lib().atoma_moe_experts(C.byref(a), C.byref(eo), C.byref(pr), _s())
+    _check()
+    x = torch.zeros((T, W), dtype=torch.float32, device=h.device)
+    ga = _lib.GatedResidualArgs()
+    ga.expert_out, ga.pair_row, ga.top, ga.x = eo.value, pr.value, top, _p(x)
+    ga.T, ga.width, ga.groups, ga.eps, ga.dtype = T, W, 1, 1e-5, code
+    _lib.lib().atoma_gated_residual_norm(C.byref(ga), _s())
+    _check()
+    torch.cuda.synchronize()      # ws is released on return
+    return x
+
+
+def finish_logits_greedy(logits, scale, softcap):
+    R, V = logits.shape
+    out = torch.empty((R, V), dtype=torch.float32, device=logits.device)
+    tok = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    _lib.lib().atoma_finish_logits_greedy(_p(logits), _p(out), _p(tok), R, V, scale, softcap, _CODES[logits.dtype], _s())
+    _check()
+    return out, tok
