@@ -11,6 +11,7 @@
 // tiles that start at the window's first key, so a query's result does not depend on the batch around it.
 #include "common.cuh"
 #include "hybrid_common.cuh"
+#include "tc_products.cuh"
 
 #include "atoma_hybrid.h"
 
@@ -242,6 +243,234 @@ __global__ void __launch_bounds__(kLatThreads) latent_attn_general_kernel(const 
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Attention on tensor cores (bfloat16 cache): a CTA owns 16 * MT consecutive (query, head) rows of ONE sequence — for a
+// decoded token its heads, for a prompt's portion several queries with all their heads — and walks the keys those rows can
+// see in tiles of 32, staged once in shared memory (cp.async, double buffered) and used as BOTH operands: S = Q C^T reads
+// the tile as stored (keys x latent), O += P C reads it transposed (ldmatrix.trans).  Per tile: each of the four warps
+// computes the scores of 8 keys for all rows (mma.sync m16n8k16, float32), the rows' running maxima / denominators are
+// updated in float32 with the window mask per row, P is rounded to bfloat16, and each warp accumulates a quarter of the
+// latent columns for all rows.  Why mma.sync and not tcgen05: the rows of a tile are H heads of a few queries (16 to 64), far
+// below a 128-row tensor-memory tile, and every row has its own window, so a larger tile would multiply mostly masked pairs.
+// ---------------------------------------------------------------------------------------------
+constexpr int kTcKeys = 32;
+
+template <int MT, int kMaxNT>   // row tiles of 16; n8 tiles of a warp's quarter of the latent columns (R <= 32 kMaxNT)
+__global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_attn_args a, int splits, float *__restrict__ partial,
+                                                             float *__restrict__ partial_ml) {
+    extern __shared__ __align__(16) unsigned char smraw[];
+    constexpr int ROWS = 16 * MT;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int H = static_cast<int>(a.H), R = static_cast<int>(a.R), bs = static_cast<int>(a.block_size);
+    const int b = blockIdx.y;
+    const int q0 = a.query_start[b], nq = a.query_start[b + 1] - q0;
+    const int row0 = blockIdx.x * ROWS, nrows = nq * H;
+    if (row0 >= nrows) return;
+    const int ldc = R + 8;
+    __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(smraw);                 // [ROWS][R + 8]
+    __nv_bfloat16 *Cs = Qs + ROWS * ldc;                                          // [2][32][R + 8]
+    float *Ss = reinterpret_cast<float *>(Cs + 2 * kTcKeys * ldc);                // [ROWS][33]
+    __nv_bfloat16 *Pb = reinterpret_cast<__nv_bfloat16 *>(Ss + ROWS * 33);        // [ROWS][40]
+    float *m_s = reinterpret_cast<float *>(Pb + ROWS * 40);
+    float *l_s = m_s + ROWS, *f_s = l_s + ROWS;
+    int *p_s = reinterpret_cast<int *>(f_s + ROWS), *lo_s = p_s + ROWS;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int32_t *bt = a.block_tables + static_cast<int64_t>(b) * a.max_blocks;
+    const __nv_bfloat16 *cache = static_cast<const __nv_bfloat16 *>(a.latent_cache);
+    const int split = blockIdx.z;
+    for (int r = tid; r < ROWS; r += 128) {
+        const int gr = row0 + r;
+        int p = -1, lo = 0;
+        float m = -INFINITY, l = 0.f;
+        if (gr < nrows) {
+            p = static_cast<int>(a.positions[q0 + gr / H]);
+            lo = a.window > 0 ? max(0, p - static_cast<int>(a.window) + 1) : 0;
+            if (split == 0 && a.sink) {
+                m = a.sink[gr % H];
+                l = 1.f;
+            }
+        }
+        p_s[r] = p;
+        lo_s[r] = lo;
+        m_s[r] = m;
+        l_s[r] = l;
+    }
+    // queries -> bfloat16 rows (rows of one sequence are contiguous in q_lat: (token, head) flattened)
+    const float *q = a.q_lat + (static_cast<int64_t>(q0) * H + row0) * R;
+    for (int i = tid; i < ROWS * (R / 4); i += 128) {
+        const int r = i / (R / 4), c = (i % (R / 4)) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row0 + r < nrows) v = *reinterpret_cast<const float4 *>(q + static_cast<int64_t>(r) * R + c);
+        uint2 w;
+        w.x = pack2<__nv_bfloat16>(v.x, v.y);
+        w.y = pack2<__nv_bfloat16>(v.z, v.w);
+        *reinterpret_cast<uint2 *>(Qs + r * ldc + c) = w;
+    }
+    // keys of the CTA: from the first row's window start to the last valid row's position
+    const int first_p = static_cast<int>(a.positions[q0 + row0 / H]);
+    const int last_p = static_cast<int>(a.positions[q0 + (min(row0 + ROWS, nrows) - 1) / H]);
+    int k_lo = a.window > 0 ? max(0, first_p - static_cast<int>(a.window) + 1) : 0, k_hi = last_p + 1;
+    if (splits > 1) {
+        const int n = k_hi - k_lo;
+        const int per = ((n + splits - 1) / splits + kTcKeys - 1) / kTcKeys * kTcKeys;
+        k_lo = min(k_hi, k_lo + split * per);
+        k_hi = min(k_hi, k_lo + per);
+    }
+    const int chunks = R / 8;   // 16-byte pieces of a latent row
+    auto stage = [&](int j0, int buf) {
+        __nv_bfloat16 *dst = Cs + buf * kTcKeys * ldc;
+        for (int i = tid; i < kTcKeys * chunks; i += 128) {
+            const int jj = i / chunks, c = (i % chunks) * 8, j = j0 + jj;
+            const bool in = j < k_hi;
+            const __nv_bfloat16 *src = in ? cache + (static_cast<int64_t>(bt[j / bs]) * bs + j % bs) * R + c : cache;
+            cp_async_16(smem_u32(dst + jj * ldc + c), src, in ? 16 : 0);
+        }
+        cp_async_commit();
+    };
+    const int NT = R / 32;
+    float acc[MT][kMaxNT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < kMaxNT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.f;
+    const int g = lane >> 2, t4 = lane & 3;
+    if (k_lo < k_hi) stage(k_lo, 0);
+    int it = 0;
+    for (int j0 = k_lo; j0 < k_hi; j0 += kTcKeys, ++it) {
+        const int buf = it & 1;
+        cp_async_wait_all();
+        __syncthreads();
+        if (j0 + kTcKeys < k_hi) stage(j0 + kTcKeys, buf ^ 1);
+        const __nv_bfloat16 *C = Cs + buf * kTcKeys * ldc;
+        // ---- scores of this warp's 8 keys for all rows ----
+        {
+            float sc[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[mt][e] = 0.f;
+            for (int kk = 0; kk < R; kk += 32) {
+                uint32_t bf[4];
+                ldmatrix_x4(bf, smem_u32(C + (warp * 8 + (lane & 7)) * ldc + kk + (lane >> 3) * 8));
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    uint32_t af[4];
+                    ldmatrix_x4(af, smem_u32(Qs + (mt * 16 + (lane & 15)) * ldc + kk + (lane >> 4) * 8));
+                    Mma16816<__nv_bfloat16>::run(sc[mt], af, bf[0], bf[1]);
+                    ldmatrix_x4(af, smem_u32(Qs + (mt * 16 + (lane & 15)) * ldc + kk + 16 + (lane >> 4) * 8));
+                    Mma16816<__nv_bfloat16>::run(sc[mt], af, bf[2], bf[3]);
+                }
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                float *s0 = Ss + (mt * 16 + g) * 33 + warp * 8 + 2 * t4;
+                s0[0] = sc[mt][0];
+                s0[1] = sc[mt][1];
+                s0[8 * 33] = sc[mt][2];
+                s0[8 * 33 + 1] = sc[mt][3];
+            }
+        }
+        __syncthreads();
+        // ---- running softmax of the rows (lane = key) ----
+        for (int r = warp; r < ROWS; r += 4) {
+            const int j = j0 + lane;
+            const bool vis = j < k_hi && j >= lo_s[r] && j <= p_s[r];
+            const float s = vis ? Ss[r * 33 + lane] * a.scale : -INFINITY;
+            float mx = s;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_old = m_s[r];
+            const float m_new = fmaxf(m_old, mx);
+            const float e = vis ? __expf(s - m_new) : 0.f;
+            float sum = e;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const float f = m_old == -INFINITY ? 0.f : __expf(m_old - m_new);
+            Pb[r * 40 + lane] = __float2bfloat16_rn(e);
+            __syncwarp();
+            if (lane == 0) {
+                m_s[r] = m_new;
+                l_s[r] = l_s[r] * f + sum;
+                f_s[r] = f;
+            }
+        }
+        __syncthreads();
+        // ---- this warp's quarter of the latent columns for all rows ----
+        const int col0 = warp * (R / 4);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            const float f0 = f_s[mt * 16 + g], f1 = f_s[mt * 16 + g + 8];
+#pragma unroll
+            for (int nt = 0; nt < kMaxNT; ++nt)
+                if (nt < NT) {
+                    acc[mt][nt][0] *= f0;
+                    acc[mt][nt][1] *= f0;
+                    acc[mt][nt][2] *= f1;
+                    acc[mt][nt][3] *= f1;
+                }
+        }
+#pragma unroll
+        for (int kk = 0; kk < kTcKeys; kk += 16) {
+            uint32_t pf[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(pf[mt], smem_u32(Pb + (mt * 16 + (lane & 15)) * 40 + kk + (lane >> 4) * 8));
+#pragma unroll
+            for (int nj = 0; nj < kMaxNT / 2; ++nj)
+                if (2 * nj < NT) {
+                    uint32_t bf[4];
+                    ldmatrix_x4_trans(bf, smem_u32(C + (kk + (lane & 7) + ((lane >> 3) & 1) * 8) * ldc + col0 + nj * 16 + (lane >> 4) * 8));
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        Mma16816<__nv_bfloat16>::run(acc[mt][2 * nj], pf[mt], bf[0], bf[1]);
+                        Mma16816<__nv_bfloat16>::run(acc[mt][2 * nj + 1], pf[mt], bf[2], bf[3]);
+                    }
+                }
+        }
+    }
+    __syncthreads();
+    // ---- results: row (token, head) -> out[(token * H + head) * R + col] ----
+    const int col0 = warp * (R / 4);
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = mt * 16 + g + half * 8, gr = row0 + r;
+            if (gr >= nrows) continue;
+            const int64_t flat = static_cast<int64_t>(q0) * H + gr;    // token * H + head
+            if (partial) {
+                float *o = partial + ((flat / H) * splits + split) * H * R + (flat % H) * R;
+#pragma unroll
+                for (int nt = 0; nt < kMaxNT; ++nt)
+                    if (nt < NT) {
+                        o[col0 + nt * 8 + 2 * t4] = acc[mt][nt][half * 2];
+                        o[col0 + nt * 8 + 2 * t4 + 1] = acc[mt][nt][half * 2 + 1];
+                    }
+                if (warp == 0 && t4 == 0) {
+                    float *ml = partial_ml + (((flat / H) * splits + split) * H + flat % H) * 2;
+                    ml[0] = m_s[r];
+                    ml[1] = l_s[r];
+                }
+            } else {
+                const float l = l_s[r], inv = l > 0.f ? 1.f / l : 0.f;
+                float *o = a.out + flat * R;
+#pragma unroll
+                for (int nt = 0; nt < kMaxNT; ++nt)
+                    if (nt < NT) {
+                        o[col0 + nt * 8 + 2 * t4] = acc[mt][nt][half * 2] * inv;
+                        o[col0 + nt * 8 + 2 * t4 + 1] = acc[mt][nt][half * 2 + 1] * inv;
+                    }
+            }
+        }
+}
+
+size_t tc_attn_smem(int mt, int64_t R) {
+    const size_t rows = 16 * mt, ldc = R + 8;
+    return rows * ldc * 2 + 2 * kTcKeys * ldc * 2 + rows * 33 * 4 + rows * 40 * 2 + rows * 5 * 4;
+}
+
 // Splits of one query are merged in split order: M = max m_k, out = sum_k acc_k e^(m_k - M) / sum_k l_k e^(m_k - M).
 __global__ void __launch_bounds__(256) latent_split_reduce_kernel(const float *__restrict__ partial, const float *__restrict__ partial_ml,
                                                                   float *__restrict__ out, int splits, int H, int R) {
@@ -293,6 +522,24 @@ bool hyb_head_project(const void *in, const void *w, void *out, int64_t T, int64
     }
     const int M = static_cast<int>(T);
     cudaError_t e;
+    if (dtype == ATOMA_DTYPE_BF16 && !(g_hybrid_debug & 1)) {   // tensor cores: operands rounded to bfloat16, float32 accumulation
+        tc::GemmArgs p{};
+        p.a = in;
+        p.b = static_cast<const __nv_bfloat16 *>(w);
+        p.o = out;
+        p.b_zs = n * R;
+        p.M = M;
+        if (absorb) {
+            p.lda = H * n, p.a_zs = n, p.b_ks = R, p.b_ns = 1, p.ldo = H * R, p.o_zs = R, p.N = static_cast<int>(R), p.K = static_cast<int>(n);
+            const dim3 grid(static_cast<unsigned>((R + 63) / 64), static_cast<unsigned>((T + 63) / 64), static_cast<unsigned>(H));
+            e = launch_ex(tc::gemm_kernel<__nv_bfloat16, float, false>, grid, dim3(128), 0, stream, p);
+        } else {
+            p.lda = H * R, p.a_zs = R, p.b_ks = 1, p.b_ns = R, p.ldo = H * n, p.o_zs = n, p.N = static_cast<int>(n), p.K = static_cast<int>(R);
+            const dim3 grid(static_cast<unsigned>((n + 63) / 64), static_cast<unsigned>((T + 63) / 64), static_cast<unsigned>(H));
+            e = launch_ex(tc::gemm_kernel<float, __nv_bfloat16, false>, grid, dim3(128), 0, stream, p);
+        }
+        return hybrid::launched(e, "tc::gemm_kernel<head>");
+    }
     if (absorb) {
         const dim3 grid(static_cast<unsigned>((R + 63) / 64), static_cast<unsigned>((T + 63) / 64), static_cast<unsigned>(H));
 #define CALL(TT) launch_ex(head_project_kernel<TT, TT, float>, grid, dim3(256), 0, stream, static_cast<const TT *>(in), H * n, n, \
@@ -311,6 +558,57 @@ bool hyb_head_project(const void *in, const void *w, void *out, int64_t T, int64
     return hybrid::launched(e, "head_project_kernel");
 }
 
+// The tensor-core kernel takes bfloat16 caches whose latent size is a multiple of 64 up to 512 (16-byte rows for cp.async,
+// whole ldmatrix tiles per warp); everything else runs the general kernel.
+bool hyb_latent_attention_tc(const atoma_latent_attn_args &a, cudaStream_t stream, bool *taken) {
+    *taken = false;
+    if (a.dtype != ATOMA_DTYPE_BF16 || (g_hybrid_debug & 2) || a.R % 64 != 0 || a.R > 512 || !a.query_start || a.max_query_len <= 0 ||
+        (reinterpret_cast<uintptr_t>(a.latent_cache) & 15) || (reinterpret_cast<uintptr_t>(a.q_lat) & 15) ||
+        current_device_info().cc_major < 8)
+        return true;
+    *taken = true;
+    const int64_t need_rows = static_cast<int64_t>(a.max_query_len) * a.H;
+    int mt = a.R <= 256 ? 4 : 2;                                   // MT * R <= 1024: accumulators fit the register file
+    while (mt > 1 && 16 * (mt / 2) >= need_rows) mt /= 2;          // no more rows than the longest portion has
+    const int rows = 16 * mt;
+    const unsigned gx = static_cast<unsigned>((need_rows + rows - 1) / rows);
+    // few CTAs over many keys (decode steps): split the keys
+    int64_t span = a.max_seq_len > 0 ? a.max_seq_len : 0;
+    if (a.window > 0) span = std::min<int64_t>(span, a.window + a.max_query_len);
+    int splits = 1;
+    const int64_t ctas = static_cast<int64_t>(gx) * a.B;
+    if (span >= 8 * kTcKeys && ctas < current_device_info().sm_count)
+        splits = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>({(2 * current_device_info().sm_count + ctas - 1) / ctas,
+                                                                         (span + 4 * kTcKeys - 1) / (4 * kTcKeys), 64})));
+    float *partial = nullptr, *partial_ml = nullptr;
+    if (splits > 1) {
+        const size_t n_acc = static_cast<size_t>(a.T) * splits * a.H * a.R, n_ml = static_cast<size_t>(a.T) * splits * a.H * 2;
+        partial = static_cast<float *>(get_workspace(stream, (n_acc + n_ml) * 4, kWorkspaceHybridAttn));
+        if (!partial) return false;
+        partial_ml = partial + n_acc;
+    }
+    const size_t smem = tc_attn_smem(mt, a.R);
+    const dim3 grid(gx, static_cast<unsigned>(a.B), static_cast<unsigned>(splits));
+    cudaError_t e;
+#define LAUNCH_MT(M, N)                                                                                                          \
+    {                                                                                                                            \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(latent_attn_tc_kernel<M, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+        e = launch_ex(latent_attn_tc_kernel<M, N>, grid, dim3(128), smem, stream, a, splits, partial, partial_ml);               \
+    }
+    if (a.R <= 256) {
+        if (mt == 4) LAUNCH_MT(4, 8) else if (mt == 2) LAUNCH_MT(2, 8) else LAUNCH_MT(1, 8)
+    } else {
+        if (mt == 2) LAUNCH_MT(2, 16) else LAUNCH_MT(1, 16)
+    }
+#undef LAUNCH_MT
+    if (!hybrid::launched(e, "latent_attn_tc_kernel")) return false;
+    if (splits == 1) return true;
+    return hybrid::launched(launch_ex(latent_split_reduce_kernel, dim3(static_cast<unsigned>(a.T)), dim3(256), 0, stream,
+                                      static_cast<const float *>(partial), static_cast<const float *>(partial_ml), a.out, splits,
+                                      static_cast<int>(a.H), static_cast<int>(a.R)),
+                            "latent_split_reduce_kernel");
+}
+
 bool hyb_latent_attention(const atoma_latent_attn_args &a, cudaStream_t stream) {
     if (a.T <= 0) return true;
     if (!hybrid::known_dtype(a.dtype, "atoma_latent_attention_paged")) return false;
@@ -319,6 +617,9 @@ bool hyb_latent_attention(const atoma_latent_attn_args &a, cudaStream_t stream) 
         set_status(kErrInvalidArg, "atoma_latent_attention_paged: null argument or empty shape");
         return false;
     }
+    bool taken = false;
+    const bool ok = hyb_latent_attention_tc(a, stream, &taken);
+    if (taken || !ok) return ok;
     if (a.H * a.R > kLatThreads * kLatMaxOut) {
         set_status(kErrUnsupported, "atoma_latent_attention_paged: heads * latent size = %lld exceeds %d", static_cast<long long>(a.H * a.R),
                    kLatThreads * kLatMaxOut);

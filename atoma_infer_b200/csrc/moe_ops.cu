@@ -9,17 +9,22 @@
 // by the residual kernel (atoma_gated_residual_norm).
 #include "common.cuh"
 #include "hybrid_common.cuh"
+#include "tc_products.cuh"
 
 #include "atoma_hybrid.h"
 
 #include <algorithm>
 
 namespace atoma {
+
+extern int g_hybrid_debug;
+
 namespace {
 
 using namespace hybrid;
 
 constexpr int kTileRows = 64;
+static_assert(kTileRows == tc::kTM, "the experts' segments are padded to the tensor-core kernel's row tile");
 constexpr int kMaxExperts = 1024;
 
 // ---------------------------------------------------------------------------------------------
@@ -294,6 +299,30 @@ bool hyb_moe_experts(const atoma_moe_args &a, const void **expert_out, const int
                            reinterpret_cast<TT *>(s.xs), static_cast<int>(a.width), static_cast<int>(a.top), static_cast<int>(a.scale_input))
     if (!hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "moe_gather_kernel")) return false;
 #undef CALL
+    const float *ow = a.scale_input ? nullptr : a.top_weight;
+    if (a.dtype == ATOMA_DTYPE_BF16 && !(g_hybrid_debug & 1)) {   // tensor cores
+        tc::GemmArgs p{};
+        p.a = s.xs, p.lda = a.width;
+        p.b = static_cast<const __nv_bfloat16 *>(a.w_gate_up), p.b_zs = 2 * a.ff * a.width, p.b_ks = 1, p.b_ns = a.width;
+        p.o = s.act, p.ldo = a.ff;
+        p.M = static_cast<int>(s.max_rows), p.N = static_cast<int>(a.ff), p.K = static_cast<int>(a.width);
+        p.tile_expert = s.tile_expert, p.meta = s.meta, p.row_pair = s.row_pair;
+        p.limit = a.limit, p.alpha = a.alpha, p.shift = a.up_shift;
+        const dim3 t1(static_cast<unsigned>((a.ff + 63) / 64), static_cast<unsigned>(s.max_tiles));
+        if (!hybrid::launched(launch_ex(tc::gemm_kernel<__nv_bfloat16, __nv_bfloat16, true>, t1, dim3(128), 0, stream, p), "tc::gemm_kernel<glu>"))
+            return false;
+        p.a = s.act, p.lda = a.ff;
+        p.b = static_cast<const __nv_bfloat16 *>(a.w_down), p.b_zs = a.width * a.ff, p.b_ns = a.ff;
+        p.o = s.y, p.ldo = a.width;
+        p.N = static_cast<int>(a.width), p.K = static_cast<int>(a.ff);
+        p.out_weight = ow;
+        const dim3 t2(static_cast<unsigned>((a.width + 63) / 64), static_cast<unsigned>(s.max_tiles));
+        if (!hybrid::launched(launch_ex(tc::gemm_kernel<__nv_bfloat16, __nv_bfloat16, false>, t2, dim3(128), 0, stream, p), "tc::gemm_kernel<down>"))
+            return false;
+        if (expert_out) *expert_out = s.y;
+        if (pair_row) *pair_row = s.pair_row;
+        return true;
+    }
     const float *no_weight = nullptr;
     const dim3 g1(static_cast<unsigned>((a.ff + 63) / 64), static_cast<unsigned>(s.max_tiles));
 #define CALL(TT) launch_ex(moe_grouped_kernel<TT, true>, g1, dim3(256), 0, stream, reinterpret_cast<const TT *>(s.xs), \
@@ -302,7 +331,6 @@ bool hyb_moe_experts(const atoma_moe_args &a, const void **expert_out, const int
                            static_cast<int>(a.ff), static_cast<int>(a.width), a.limit, a.alpha, a.up_shift)
     if (!hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "moe_grouped_kernel<glu>")) return false;
 #undef CALL
-    const float *ow = a.scale_input ? nullptr : a.top_weight;
     const dim3 g2(static_cast<unsigned>((a.width + 63) / 64), static_cast<unsigned>(s.max_tiles));
 #define CALL(TT) launch_ex(moe_grouped_kernel<TT, false>, g2, dim3(256), 0, stream, reinterpret_cast<const TT *>(s.act), \
                            static_cast<const TT *>(a.w_down), reinterpret_cast<TT *>(s.y), static_cast<const int32_t *>(s.tile_expert), \

@@ -224,46 +224,58 @@ def paged_latents(g, seqs, R, bs, dtype, extra_pages=3):
             torch.tensor(tseq, dtype=torch.int32, device=DEV), lat)
 
 
+def uses_tensor_cores(dtype, R, general):
+    """bfloat16 caches with a latent size that is a multiple of 64 run the tensor-core kernel (queries and weights rounded to
+    bfloat16 there); everything else, and everything under debug flag 2, runs the general float32 kernel."""
+    return dtype == torch.bfloat16 and R % 64 == 0 and not general
+
+
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("H,R,window,sink", [(3, 16, 20, True), (1, 40, 0, True), (6, 24, 7, False), (4, 64, 33, True), (2, 8, 1, True)])
-def test_latent_attention_on_a_mixed_batch(dtype, H, R, window, sink):
+@pytest.mark.parametrize("general", [False, True])
+@pytest.mark.parametrize("H,R,window,sink", [(3, 16, 20, True), (1, 40, 0, True), (6, 24, 7, False), (4, 64, 33, True), (2, 8, 1, True),
+                                             (5, 128, 20, True), (16, 64, 0, False), (3, 512, 50, True), (20, 192, 9, True)])
+def test_latent_attention_on_a_mixed_batch(dtype, general, H, R, window, sink):
     g = torch.Generator().manual_seed(7)
     seqs = [(0, 45), (37, 1), (16, 2), (90, 1), (0, 1), (15, 17)]
     cache, bt, pos, tseq, lat = paged_latents(g, seqs, R, 4, dtype)
     T = pos.numel()
-    q = torch.randn(T, H, R, generator=g)
+    q = torch.randn(T, H, R, generator=g) * (4.0 / math.sqrt(R))
     sk = torch.randn(H, generator=g) if sink else None
+    if general:
+        _ops().debug_flags(2)
     got = _ops().latent_attention_paged(q.to(DEV), cache, pos, tseq, bt, sk.to(DEV) if sink else None, H, R, 4, window, 0.3,
                                         max(n for _, n in seqs))
     want = torch.stack([latent_attention_plain(q[t].double(), lat[int(tseq[t])].double(), sk.double() if sink else None, 0.3, window,
                                                int(pos[t])) for t in range(T)])
-    assert nerr(got, want) < 3e-6
+    assert nerr(got, want) < (1e-2 if uses_tensor_cores(dtype, R, general) else 3e-6)
 
 
 @pytest.mark.parametrize("dtype", BOTH)
+@pytest.mark.parametrize("R", [32, 64])
 @pytest.mark.parametrize("window", [0, 150, 700])
-def test_latent_attention_decoding_over_long_contexts_with_split_keys(dtype, window):
+def test_latent_attention_decoding_over_long_contexts_with_split_keys(dtype, R, window):
     g = torch.Generator().manual_seed(8)
-    H, R = 5, 32
+    H = 5
     seqs = [(900, 1), (3, 1), (0, 1), (257, 1)]
     cache, bt, pos, tseq, lat = paged_latents(g, seqs, R, 16, dtype)
-    q = torch.randn(4, H, R, generator=g)
+    q = torch.randn(4, H, R, generator=g) * (4.0 / math.sqrt(R))
     sk = torch.randn(H, generator=g)
     want = torch.stack([latent_attention_plain(q[t].double(), lat[t].double(), sk.double(), 0.2, window, int(pos[t])) for t in range(4)])
     got = _ops().latent_attention_paged(q.to(DEV), cache, pos, tseq, bt, sk.to(DEV), H, R, 16, window, 0.2, 1)
-    assert nerr(got, want) < 3e-6
-    _ops().debug_flags(2)          # unsplit
+    assert nerr(got, want) < (1e-2 if uses_tensor_cores(dtype, R, False) else 3e-6)
+    _ops().debug_flags(2)          # the general kernel, unsplit
     one = _ops().latent_attention_paged(q.to(DEV), cache, pos, tseq, bt, sk.to(DEV), H, R, 16, window, 0.2, 1)
     assert nerr(one, want) < 3e-6
 
 
 @pytest.mark.parametrize("dtype", BOTH)
+@pytest.mark.parametrize("R", [16, 64])
 @pytest.mark.parametrize("decode", [False, True])
-def test_one_loud_key_is_seen_just_inside_the_window_and_not_just_outside(dtype, decode):
+def test_one_loud_key_is_seen_just_inside_the_window_and_not_just_outside(dtype, R, decode):
     """All latents are small but one, whose score towers over the rest when it is visible: the output then IS that latent.
     Placed at the window's first key, one before it, at page borders, hundreds of keys back, at the query, at position 0."""
     g = torch.Generator().manual_seed(9)
-    H, R, bs, window, L = 2, 16, 8, 96, 400
+    H, bs, window, L = 2, 8, 96, 400
     u = torch.zeros(R)
     u[3] = 1.0
     for i, loud in [(399, 399 - 95), (399, 399 - 96), (399, 304), (399, 303), (200, 105), (200, 104), (95, 0), (96, 0), (399, 399),
@@ -286,7 +298,7 @@ def test_one_loud_key_is_seen_just_inside_the_window_and_not_just_outside(dtype,
         visible = 0 <= i - loud < window
         assert (abs(float(got[0, 3]) - 8.0) < 1e-3) == visible, (i, loud)
         want = latent_attention_plain(q[-1].double(), c.double(), torch.zeros(H, dtype=F64), 1.0, window, i)
-        assert (got.double() - want).abs().max() < 1e-5, (i, loud)
+        assert (got.double() - want).abs().max() < (2e-3 if uses_tensor_cores(dtype, R, False) else 1e-5), (i, loud)
 
 
 def test_the_sink_takes_its_share_of_the_weights():
