@@ -270,7 +270,7 @@ def moe_experts(h, top_expert, top_weight, w_gate_up, w_down, limit, alpha, up_s
     ga.T, ga.width, ga.groups, ga.eps, ga.dtype = T, W, 1, 1e-5, code
     _lib.lib().atoma_gated_residual_norm(C.byref(ga), _s())
     _check()
-    torch.cuda.synchronize()      # ws is released on return
+    x._workspace = ws             # the kernels may still be running: the workspace lives as long as the result
     return x
 
 
