@@ -247,19 +247,24 @@ __global__ void __launch_bounds__(kLatThreads) latent_attn_general_kernel(const 
 // Attention on tensor cores (bfloat16 cache): a CTA owns 16 * MT consecutive (query, head) rows of ONE sequence — for a
 // decoded token its heads, for a prompt's portion several queries with all their heads — and walks the keys those rows can
 // see in tiles of 32, staged once in shared memory (cp.async, double buffered) and used as BOTH operands: S = Q C^T reads
-// the tile as stored (keys x latent), O += P C reads it transposed (ldmatrix.trans).  Per tile: each of the four warps
-// computes the scores of 8 keys for all rows (mma.sync m16n8k16, float32), the rows' running maxima / denominators are
-// updated in float32 with the window mask per row, P is rounded to bfloat16, and each warp accumulates a quarter of the
-// latent columns for all rows.  Why mma.sync and not tcgen05: the rows of a tile are H heads of a few queries (16 to 64), far
-// below a 128-row tensor-memory tile, and every row has its own window, so a larger tile would multiply mostly masked pairs.
+// the tile as stored (keys x latent), O += P C reads it transposed (ldmatrix.trans).  Per tile: the score product is split
+// over the warps along the LATENT axis (a warp multiplies all rows by 32 or 16 keys over a quarter of the latent columns, so
+// that every fragment it loads feeds several mma.sync m16n8k16), the four partial score tiles are summed while the rows'
+// running maxima / denominators are updated in float32 with the window mask per row, P is rounded to bfloat16, and each
+// warp accumulates its share of the latent columns for all rows.  Why mma.sync and not tcgen05: the rows of a tile are H heads
+// of a few queries (16 to 64), far below a 128-row tensor-memory tile, and every row has its own window, so a larger tile
+// would multiply mostly masked pairs.
 // ---------------------------------------------------------------------------------------------
 constexpr int kTcKeys = 32;
+constexpr int kTcMaxNT = 8;      // n8 tiles of a warp's share of the latent columns: R <= 64 * warps
 
-template <int MT, int kMaxNT>   // row tiles of 16; n8 tiles of a warp's quarter of the latent columns (R <= 32 kMaxNT)
-__global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_attn_args a, int splits, float *__restrict__ partial,
-                                                             float *__restrict__ partial_ml) {
+template <int MT, int NW>   // row tiles of 16; warps (4 or 8)
+__global__ void __launch_bounds__(32 * NW) latent_attn_tc_kernel(const atoma_latent_attn_args a, int splits, float *__restrict__ partial,
+                                                                 float *__restrict__ partial_ml) {
     extern __shared__ __align__(16) unsigned char smraw[];
-    constexpr int ROWS = 16 * MT;
+    constexpr int ROWS = 16 * MT, NTHR = 32 * NW;
+    constexpr int KEYS_W = NW == 8 ? 16 : 32;      // keys a warp multiplies in the score product
+    constexpr int NKT = KEYS_W / 8;
     pdl_launch_dependents();
     pdl_wait();
     const int H = static_cast<int>(a.H), R = static_cast<int>(a.R), bs = static_cast<int>(a.block_size);
@@ -270,8 +275,8 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
     const int ldc = R + 8;
     __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(smraw);                 // [ROWS][R + 8]
     __nv_bfloat16 *Cs = Qs + ROWS * ldc;                                          // [2][32][R + 8]
-    float *Ss = reinterpret_cast<float *>(Cs + 2 * kTcKeys * ldc);                // [ROWS][33]
-    __nv_bfloat16 *Pb = reinterpret_cast<__nv_bfloat16 *>(Ss + ROWS * 33);        // [ROWS][40]
+    float *Sp = reinterpret_cast<float *>(Cs + 2 * kTcKeys * ldc);                // [4][ROWS][33] partial scores per latent quarter
+    __nv_bfloat16 *Pb = reinterpret_cast<__nv_bfloat16 *>(Sp + 4 * ROWS * 33);    // [ROWS][40]
     float *m_s = reinterpret_cast<float *>(Pb + ROWS * 40);
     float *l_s = m_s + ROWS, *f_s = l_s + ROWS;
     int *p_s = reinterpret_cast<int *>(f_s + ROWS), *lo_s = p_s + ROWS;
@@ -279,7 +284,7 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
     const int32_t *bt = a.block_tables + static_cast<int64_t>(b) * a.max_blocks;
     const __nv_bfloat16 *cache = static_cast<const __nv_bfloat16 *>(a.latent_cache);
     const int split = blockIdx.z;
-    for (int r = tid; r < ROWS; r += 128) {
+    for (int r = tid; r < ROWS; r += NTHR) {
         const int gr = row0 + r;
         int p = -1, lo = 0;
         float m = -INFINITY, l = 0.f;
@@ -298,7 +303,7 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
     }
     // queries -> bfloat16 rows (rows of one sequence are contiguous in q_lat: (token, head) flattened)
     const float *q = a.q_lat + (static_cast<int64_t>(q0) * H + row0) * R;
-    for (int i = tid; i < ROWS * (R / 4); i += 128) {
+    for (int i = tid; i < ROWS * (R / 4); i += NTHR) {
         const int r = i / (R / 4), c = (i % (R / 4)) * 4;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (row0 + r < nrows) v = *reinterpret_cast<const float4 *>(q + static_cast<int64_t>(r) * R + c);
@@ -320,7 +325,7 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
     const int chunks = R / 8;   // 16-byte pieces of a latent row
     auto stage = [&](int j0, int buf) {
         __nv_bfloat16 *dst = Cs + buf * kTcKeys * ldc;
-        for (int i = tid; i < kTcKeys * chunks; i += 128) {
+        for (int i = tid; i < kTcKeys * chunks; i += NTHR) {
             const int jj = i / chunks, c = (i % chunks) * 8, j = j0 + jj;
             const bool in = j < k_hi;
             const __nv_bfloat16 *src = in ? cache + (static_cast<int64_t>(bt[j / bs]) * bs + j % bs) * R + c : cache;
@@ -328,15 +333,17 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
         }
         cp_async_commit();
     };
-    const int NT = R / 32;
-    float acc[MT][kMaxNT][4];
+    const int NT = R / (8 * NW);               // n8 tiles of this warp's output columns (even)
+    float acc[MT][kTcMaxNT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < kMaxNT; ++nt)
+        for (int nt = 0; nt < kTcMaxNT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.f;
     const int g = lane >> 2, t4 = lane & 3;
+    const int kq = warp & 3, key0 = NW == 8 ? (warp >> 2) * 16 : 0;
+    const int col0 = warp * (R / NW);
     if (k_lo < k_hi) stage(k_lo, 0);
     int it = 0;
     for (int j0 = k_lo; j0 < k_hi; j0 += kTcKeys, ++it) {
@@ -345,40 +352,50 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
         __syncthreads();
         if (j0 + kTcKeys < k_hi) stage(j0 + kTcKeys, buf ^ 1);
         const __nv_bfloat16 *C = Cs + buf * kTcKeys * ldc;
-        // ---- scores of this warp's 8 keys for all rows ----
+        // ---- partial scores: all rows x this warp's keys over its quarter of the latent columns ----
         {
-            float sc[MT][4];
+            float sc[MT][NKT][4];
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) sc[mt][e] = 0.f;
-            for (int kk = 0; kk < R; kk += 32) {
-                uint32_t bf[4];
-                ldmatrix_x4(bf, smem_u32(C + (warp * 8 + (lane & 7)) * ldc + kk + (lane >> 3) * 8));
+                for (int n = 0; n < NKT; ++n)
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    uint32_t af[4];
-                    ldmatrix_x4(af, smem_u32(Qs + (mt * 16 + (lane & 15)) * ldc + kk + (lane >> 4) * 8));
-                    Mma16816<__nv_bfloat16>::run(sc[mt], af, bf[0], bf[1]);
-                    ldmatrix_x4(af, smem_u32(Qs + (mt * 16 + (lane & 15)) * ldc + kk + 16 + (lane >> 4) * 8));
-                    Mma16816<__nv_bfloat16>::run(sc[mt], af, bf[2], bf[3]);
+                    for (int e = 0; e < 4; ++e) sc[mt][n][e] = 0.f;
+            const int kend = (kq + 1) * (R / 4);
+            for (int kk = kq * (R / 4); kk < kend; kk += 16) {
+                uint32_t af[MT][4];
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(af[mt], smem_u32(Qs + (mt * 16 + (lane & 15)) * ldc + kk + (lane >> 4) * 8));
+#pragma unroll
+                for (int nb = 0; nb < NKT / 2; ++nb) {
+                    uint32_t bf[4];
+                    ldmatrix_x4(bf, smem_u32(C + (key0 + nb * 16 + (lane & 7) + (lane >> 4) * 8) * ldc + kk + ((lane >> 3) & 1) * 8));
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        Mma16816<__nv_bfloat16>::run(sc[mt][2 * nb], af[mt], bf[0], bf[1]);
+                        Mma16816<__nv_bfloat16>::run(sc[mt][2 * nb + 1], af[mt], bf[2], bf[3]);
+                    }
                 }
             }
+            float *sp = Sp + kq * ROWS * 33;
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                float *s0 = Ss + (mt * 16 + g) * 33 + warp * 8 + 2 * t4;
-                s0[0] = sc[mt][0];
-                s0[1] = sc[mt][1];
-                s0[8 * 33] = sc[mt][2];
-                s0[8 * 33 + 1] = sc[mt][3];
-            }
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int n = 0; n < NKT; ++n) {
+                    float *s0 = sp + (mt * 16 + g) * 33 + key0 + n * 8 + 2 * t4;
+                    s0[0] = sc[mt][n][0];
+                    s0[1] = sc[mt][n][1];
+                    s0[8 * 33] = sc[mt][n][2];
+                    s0[8 * 33 + 1] = sc[mt][n][3];
+                }
         }
         __syncthreads();
-        // ---- running softmax of the rows (lane = key) ----
-        for (int r = warp; r < ROWS; r += 4) {
+        // ---- running softmax of the rows (lane = key); the four partial tiles are summed in a fixed order ----
+        for (int r = warp; r < ROWS; r += NW) {
             const int j = j0 + lane;
             const bool vis = j < k_hi && j >= lo_s[r] && j <= p_s[r];
-            const float s = vis ? Ss[r * 33 + lane] * a.scale : -INFINITY;
+            const float raw = (Sp[r * 33 + lane] + Sp[(ROWS + r) * 33 + lane]) + (Sp[(2 * ROWS + r) * 33 + lane] + Sp[(3 * ROWS + r) * 33 + lane]);
+            const float s = vis ? raw * a.scale : -INFINITY;
             float mx = s;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -398,13 +415,12 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
             }
         }
         __syncthreads();
-        // ---- this warp's quarter of the latent columns for all rows ----
-        const int col0 = warp * (R / 4);
+        // ---- this warp's share of the latent columns for all rows ----
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
             const float f0 = f_s[mt * 16 + g], f1 = f_s[mt * 16 + g + 8];
 #pragma unroll
-            for (int nt = 0; nt < kMaxNT; ++nt)
+            for (int nt = 0; nt < kTcMaxNT; ++nt)
                 if (nt < NT) {
                     acc[mt][nt][0] *= f0;
                     acc[mt][nt][1] *= f0;
@@ -418,7 +434,7 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) ldmatrix_x4(pf[mt], smem_u32(Pb + (mt * 16 + (lane & 15)) * 40 + kk + (lane >> 4) * 8));
 #pragma unroll
-            for (int nj = 0; nj < kMaxNT / 2; ++nj)
+            for (int nj = 0; nj < kTcMaxNT / 2; ++nj)
                 if (2 * nj < NT) {
                     uint32_t bf[4];
                     ldmatrix_x4_trans(bf, smem_u32(C + (kk + (lane & 7) + ((lane >> 3) & 1) * 8) * ldc + col0 + nj * 16 + (lane >> 4) * 8));
@@ -432,7 +448,6 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
     }
     __syncthreads();
     // ---- results: row (token, head) -> out[(token * H + head) * R + col] ----
-    const int col0 = warp * (R / 4);
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -443,7 +458,7 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
             if (partial) {
                 float *o = partial + ((flat / H) * splits + split) * H * R + (flat % H) * R;
 #pragma unroll
-                for (int nt = 0; nt < kMaxNT; ++nt)
+                for (int nt = 0; nt < kTcMaxNT; ++nt)
                     if (nt < NT) {
                         o[col0 + nt * 8 + 2 * t4] = acc[mt][nt][half * 2];
                         o[col0 + nt * 8 + 2 * t4 + 1] = acc[mt][nt][half * 2 + 1];
@@ -457,7 +472,7 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
                 const float l = l_s[r], inv = l > 0.f ? 1.f / l : 0.f;
                 float *o = a.out + flat * R;
 #pragma unroll
-                for (int nt = 0; nt < kMaxNT; ++nt)
+                for (int nt = 0; nt < kTcMaxNT; ++nt)
                     if (nt < NT) {
                         o[col0 + nt * 8 + 2 * t4] = acc[mt][nt][half * 2] * inv;
                         o[col0 + nt * 8 + 2 * t4 + 1] = acc[mt][nt][half * 2 + 1] * inv;
@@ -468,28 +483,37 @@ __global__ void __launch_bounds__(128) latent_attn_tc_kernel(const atoma_latent_
 
 size_t tc_attn_smem(int mt, int64_t R) {
     const size_t rows = 16 * mt, ldc = R + 8;
-    return rows * ldc * 2 + 2 * kTcKeys * ldc * 2 + rows * 33 * 4 + rows * 40 * 2 + rows * 5 * 4;
+    return rows * ldc * 2 + 2 * kTcKeys * ldc * 2 + 4 * rows * 33 * 4 + rows * 40 * 2 + rows * 5 * 4;
 }
 
-// Splits of one query are merged in split order: M = max m_k, out = sum_k acc_k e^(m_k - M) / sum_k l_k e^(m_k - M).
-__global__ void __launch_bounds__(256) latent_split_reduce_kernel(const float *__restrict__ partial, const float *__restrict__ partial_ml,
+// Splits of one (query, head) are merged in split order: M = max m_k, out = sum_k acc_k e^(m_k - M) / sum_k l_k e^(m_k - M).
+// One CTA per (token, head); the factors are formed once per CTA.
+__global__ void __launch_bounds__(128) latent_split_reduce_kernel(const float *__restrict__ partial, const float *__restrict__ partial_ml,
                                                                   float *__restrict__ out, int splits, int H, int R) {
+    __shared__ float f_s[64];
+    __shared__ float den_s;
     pdl_launch_dependents();
     pdl_wait();
-    const int64_t t = blockIdx.x;
-    for (int i = threadIdx.x; i < H * R; i += blockDim.x) {
-        const int h = i / R;
+    const int64_t t = blockIdx.x / H;
+    const int h = blockIdx.x % H;
+    if (threadIdx.x == 0) {
         float M = -INFINITY;
         for (int k = 0; k < splits; ++k) M = fmaxf(M, partial_ml[((t * splits + k) * H + h) * 2]);
-        float num = 0.f, den = 0.f;
+        float den = 0.f;
         for (int k = 0; k < splits; ++k) {
             const float m = partial_ml[((t * splits + k) * H + h) * 2];
-            if (m == -INFINITY) continue;
-            const float f = expf(m - M);
-            num = fmaf(partial[(t * splits + k) * H * R + i], f, num);
+            const float f = m == -INFINITY ? 0.f : expf(m - M);
+            f_s[k] = f;
             den = fmaf(partial_ml[((t * splits + k) * H + h) * 2 + 1], f, den);
         }
-        out[t * H * R + i] = den > 0.f ? num / den : 0.f;
+        den_s = den;
+    }
+    __syncthreads();
+    const float inv = den_s > 0.f ? 1.f / den_s : 0.f;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) {
+        float num = 0.f;
+        for (int k = 0; k < splits; ++k) num = fmaf(partial[((t * splits + k) * H + h) * R + i], f_s[k], num);
+        out[(t * H + h) * R + i] = num * inv;
     }
 }
 
@@ -558,17 +582,19 @@ bool hyb_head_project(const void *in, const void *w, void *out, int64_t T, int64
     return hybrid::launched(e, "head_project_kernel");
 }
 
-// The tensor-core kernel takes bfloat16 caches whose latent size is a multiple of 64 up to 512 (16-byte rows for cp.async,
-// whole ldmatrix tiles per warp); everything else runs the general kernel.
+// The tensor-core kernel takes bfloat16 caches whose latent size is a multiple of 64 up to 256 (four warps) or a multiple of
+// 128 up to 512 (eight warps): 16-byte rows for cp.async, whole ldmatrix tiles per warp, at most 8 accumulator tiles per
+// warp and row tile.  Everything else runs the general kernel.
 bool hyb_latent_attention_tc(const atoma_latent_attn_args &a, cudaStream_t stream, bool *taken) {
     *taken = false;
-    if (a.dtype != ATOMA_DTYPE_BF16 || (g_hybrid_debug & 2) || a.R % 64 != 0 || a.R > 512 || !a.query_start || a.max_query_len <= 0 ||
+    const bool four = a.R % 64 == 0 && a.R <= 256, eight = a.R % 128 == 0 && a.R > 256 && a.R <= 512;
+    if (a.dtype != ATOMA_DTYPE_BF16 || (g_hybrid_debug & 2) || !(four || eight) || !a.query_start || a.max_query_len <= 0 ||
         (reinterpret_cast<uintptr_t>(a.latent_cache) & 15) || (reinterpret_cast<uintptr_t>(a.q_lat) & 15) ||
         current_device_info().cc_major < 8)
         return true;
     *taken = true;
     const int64_t need_rows = static_cast<int64_t>(a.max_query_len) * a.H;
-    int mt = a.R <= 256 ? 4 : 2;                                   // MT * R <= 1024: accumulators fit the register file
+    int mt = 4;
     while (mt > 1 && 16 * (mt / 2) >= need_rows) mt /= 2;          // no more rows than the longest portion has
     const int rows = 16 * mt;
     const unsigned gx = static_cast<unsigned>((need_rows + rows - 1) / rows);
@@ -590,20 +616,20 @@ bool hyb_latent_attention_tc(const atoma_latent_attn_args &a, cudaStream_t strea
     const size_t smem = tc_attn_smem(mt, a.R);
     const dim3 grid(gx, static_cast<unsigned>(a.B), static_cast<unsigned>(splits));
     cudaError_t e;
-#define LAUNCH_MT(M, N)                                                                                                          \
+#define LAUNCH_TC(M, N)                                                                                                          \
     {                                                                                                                            \
         if (smem > 48 * 1024) cudaFuncSetAttribute(latent_attn_tc_kernel<M, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
-        e = launch_ex(latent_attn_tc_kernel<M, N>, grid, dim3(128), smem, stream, a, splits, partial, partial_ml);               \
+        e = launch_ex(latent_attn_tc_kernel<M, N>, grid, dim3(32 * N), smem, stream, a, splits, partial, partial_ml);            \
     }
-    if (a.R <= 256) {
-        if (mt == 4) LAUNCH_MT(4, 8) else if (mt == 2) LAUNCH_MT(2, 8) else LAUNCH_MT(1, 8)
+    if (four) {
+        if (mt == 4) LAUNCH_TC(4, 4) else if (mt == 2) LAUNCH_TC(2, 4) else LAUNCH_TC(1, 4)
     } else {
-        if (mt == 2) LAUNCH_MT(2, 16) else LAUNCH_MT(1, 16)
+        if (mt == 4) LAUNCH_TC(4, 8) else if (mt == 2) LAUNCH_TC(2, 8) else LAUNCH_TC(1, 8)
     }
-#undef LAUNCH_MT
+#undef LAUNCH_TC
     if (!hybrid::launched(e, "latent_attn_tc_kernel")) return false;
     if (splits == 1) return true;
-    return hybrid::launched(launch_ex(latent_split_reduce_kernel, dim3(static_cast<unsigned>(a.T)), dim3(256), 0, stream,
+    return hybrid::launched(launch_ex(latent_split_reduce_kernel, dim3(static_cast<unsigned>(a.T * a.H)), dim3(128), 0, stream,
                                       static_cast<const float *>(partial), static_cast<const float *>(partial_ml), a.out, splits,
                                       static_cast<int>(a.H), static_cast<int>(a.R)),
                             "latent_split_reduce_kernel");
@@ -654,7 +680,7 @@ bool hyb_latent_attention(const atoma_latent_attn_args &a, cudaStream_t stream) 
     if (!hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "latent_attn_general_kernel")) return false;
 #undef CALL
     if (splits == 1) return true;
-    return hybrid::launched(launch_ex(latent_split_reduce_kernel, dim3(static_cast<unsigned>(a.T)), dim3(256), 0, stream,
+    return hybrid::launched(launch_ex(latent_split_reduce_kernel, dim3(static_cast<unsigned>(a.T * a.H)), dim3(128), 0, stream,
                                       static_cast<const float *>(partial), static_cast<const float *>(partial_ml), a.out, splits,
                                       static_cast<int>(a.H), static_cast<int>(a.R)),
                             "latent_split_reduce_kernel");

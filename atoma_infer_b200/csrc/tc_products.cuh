@@ -5,8 +5,10 @@
 // weight stored [k][n] needs no transposed copy), O is float32 or bfloat16.  In grouped mode the row tiles belong to
 // experts (tile_expert) and B(z) is the tile's expert; with GLU the tile computes the gate and the up product of the same
 // rows and stores the clamped gated activation.
-// 64 x 64 x 32 tiles, four warps of 32 x 32; the next tile's operands are fetched into registers while the current one
-// is multiplied.  Why not tcgen05 here: the experts' row segments are known on the device only (no host read), a segment
+// 64 x 64 x 32 tiles, four warps of 32 x 32.  bfloat16 operands with contiguous, 16-byte aligned k runs (the experts' case) go
+// through a three-stage cp.async ring, so that a CTA keeps two tiles of weights in flight while it multiplies a third — at
+// decode sizes the product is a pure weight stream; otherwise the next tile's operands are fetched into registers
+// (converted / transposed there) while the current one is multiplied.  Why not tcgen05 here: the experts' row segments are known on the device only (no host read), a segment
 // is often a handful of rows, and the per-head products have K or N of one head (tens to a few hundred) — tiles of 64 rows
 // with operands staged by plain loads fit both; a 128-row tensor-memory tile would be mostly padding.
 #pragma once
@@ -31,7 +33,9 @@ struct GemmArgs {
     float limit, alpha, shift; // GLU epilogue
 };
 
-constexpr int kTM = 64, kTN = 64, kTK = 32, kLd = kTK + 8;
+constexpr int kTM = 64, kTN = 64, kTK = 32, kLd = kTK + 8, kStages = 3;
+
+__device__ __forceinline__ void cp_async_wait_two() { asm volatile("cp.async.wait_group 2;" ::: "memory"); }
 
 __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
     uint4 r;
@@ -63,7 +67,7 @@ __device__ __forceinline__ uint4 fetch8(const TS *p, int64_t stride, int nvalid,
 
 template <typename TA, typename TO, bool GLU>
 __global__ void __launch_bounds__(128) gemm_kernel(const GemmArgs p) {
-    __shared__ __align__(16) __nv_bfloat16 As[kTM][kLd], Bs[kTN][kLd], Us[GLU ? kTN : 1][kLd];
+    __shared__ __align__(16) __nv_bfloat16 As[kStages][kTM][kLd], Bs[kStages][kTN][kLd], Us[GLU ? kStages : 1][GLU ? kTN : 1][kLd];
     pdl_launch_dependents();
     pdl_wait();
     const int tile_m = blockIdx.y;
@@ -109,32 +113,28 @@ __global__ void __launch_bounds__(128) gemm_kernel(const GemmArgs p) {
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
             const int c = tid + s * 128;
-            *reinterpret_cast<uint4 *>(&As[c >> 2][(c & 3) * 8]) = ra[s];
+            *reinterpret_cast<uint4 *>(&As[0][c >> 2][(c & 3) * 8]) = ra[s];
             if (b_k_contig) {
-                *reinterpret_cast<uint4 *>(&Bs[c >> 2][(c & 3) * 8]) = rb[s];
-                if constexpr (GLU) *reinterpret_cast<uint4 *>(&Us[c >> 2][(c & 3) * 8]) = ru[s];
+                *reinterpret_cast<uint4 *>(&Bs[0][c >> 2][(c & 3) * 8]) = rb[s];
+                if constexpr (GLU) *reinterpret_cast<uint4 *>(&Us[0][c >> 2][(c & 3) * 8]) = ru[s];
             } else {
                 const __nv_bfloat16 *e = reinterpret_cast<const __nv_bfloat16 *>(&rb[s]);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) Bs[(c & 7) * 8 + i][c >> 3] = e[i];
+                for (int i = 0; i < 8; ++i) Bs[0][(c & 7) * 8 + i][c >> 3] = e[i];
             }
         }
     };
     float acc[2][4][4] = {}, acu[GLU ? 2 : 1][4][4] = {};
-    fetch(0);
-    for (int k0 = 0; k0 < p.K; k0 += kTK) {
-        stash();
-        __syncthreads();
-        if (k0 + kTK < p.K) fetch(k0 + kTK);
+    auto multiply = [&](int st) {
 #pragma unroll
         for (int kk = 0; kk < kTK; kk += 16) {
             uint32_t af[2][4];
 #pragma unroll
-            for (int mi = 0; mi < 2; ++mi) ldmatrix_x4(af[mi], smem_u32(&As[wm * 32 + mi * 16 + (lane & 15)][kk + (lane >> 4) * 8]));
+            for (int mi = 0; mi < 2; ++mi) ldmatrix_x4(af[mi], smem_u32(&As[st][wm * 32 + mi * 16 + (lane & 15)][kk + (lane >> 4) * 8]));
 #pragma unroll
             for (int nj = 0; nj < 2; ++nj) {
                 uint32_t bf[4];
-                ldmatrix_x4(bf, smem_u32(&Bs[wn * 32 + nj * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]));
+                ldmatrix_x4(bf, smem_u32(&Bs[st][wn * 32 + nj * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]));
 #pragma unroll
                 for (int mi = 0; mi < 2; ++mi) {
                     Mma16816<__nv_bfloat16>::run(acc[mi][2 * nj], af[mi], bf[0], bf[1]);
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(128) gemm_kernel(const GemmArgs p) {
                 }
                 if constexpr (GLU) {
                     uint32_t uf[4];
-                    ldmatrix_x4(uf, smem_u32(&Us[wn * 32 + nj * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]));
+                    ldmatrix_x4(uf, smem_u32(&Us[st][wn * 32 + nj * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]));
 #pragma unroll
                     for (int mi = 0; mi < 2; ++mi) {
                         Mma16816<__nv_bfloat16>::run(acu[mi][2 * nj], af[mi], uf[0], uf[1]);
@@ -151,7 +151,42 @@ __global__ void __launch_bounds__(128) gemm_kernel(const GemmArgs p) {
                 }
             }
         }
-        __syncthreads();
+    };
+    const bool ring = sizeof(TA) == 2 && a_vec && b_vec && b_k_contig && p.K % kTK == 0;
+    if (ring) {
+        const __nv_bfloat16 *Ab = reinterpret_cast<const __nv_bfloat16 *>(A);
+        auto issue = [&](int kt, int st) {
+#pragma unroll
+            for (int s = 0; s < 2; ++s) {
+                const int c = tid + s * 128, r = c >> 2, kc = (c & 3) * 8, k = kt * kTK + kc;
+                const bool min_ = m0 + r < p.M, nin = n0 + r < p.N;
+                cp_async_16(smem_u32(&As[st][r][kc]), min_ ? Ab + static_cast<int64_t>(m0 + r) * p.lda + k : Ab, min_ ? 16 : 0);
+                cp_async_16(smem_u32(&Bs[st][r][kc]), nin ? B + static_cast<int64_t>(n0 + r) * p.b_ns + k : B, nin ? 16 : 0);
+                if constexpr (GLU) cp_async_16(smem_u32(&Us[st][r][kc]), nin ? U + static_cast<int64_t>(n0 + r) * p.b_ns + k : B, nin ? 16 : 0);
+            }
+        };
+        const int nk = p.K / kTK;
+        issue(0, 0);
+        cp_async_commit();
+        if (nk > 1) issue(1, 1);
+        cp_async_commit();
+        for (int kt = 0; kt < nk; ++kt) {
+            if (kt + 2 < nk) issue(kt + 2, (kt + 2) % kStages);
+            cp_async_commit();          // one group per iteration, empty at the tail, so that "all but two" means tile kt
+            cp_async_wait_two();
+            __syncthreads();
+            multiply(kt % kStages);
+            __syncthreads();
+        }
+    } else {
+        fetch(0);
+        for (int k0 = 0; k0 < p.K; k0 += kTK) {
+            stash();
+            __syncthreads();
+            if (k0 + kTK < p.K) fetch(k0 + kTK);
+            multiply(0);
+            __syncthreads();
+        }
     }
     TO *O = static_cast<TO *>(p.o) + (p.tile_expert ? 0 : z * p.o_zs);
     const int g = lane >> 2, t4 = lane & 3;
