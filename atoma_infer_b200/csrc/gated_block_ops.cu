@@ -16,6 +16,7 @@ namespace {
 using namespace hybrid;
 
 constexpr int kMaxNormGroups = 64;
+constexpr int kMaxTopRows = 64;      // expert rows summed per token
 
 template <typename T>
 __global__ void __launch_bounds__(128) embed_learned_kernel(const uint32_t *__restrict__ tokens, const int64_t *__restrict__ positions,
@@ -34,6 +35,23 @@ __global__ void __launch_bounds__(128) embed_learned_kernel(const uint32_t *__re
     for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = to_f(e[c]) + to_f(q[c]);
 }
 
+// Four consecutive elements at once (8 bytes of bfloat16, 16 of float32); the caller has checked the alignment.
+__device__ __forceinline__ float4 load4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16 *p) {
+    const uint2 v = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float *p, const float4 &v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16 *p, const float4 &v) {
+    uint2 w;
+    w.x = pack2<__nv_bfloat16>(v.x, v.y);
+    w.y = pack2<__nv_bfloat16>(v.z, v.w);
+    *reinterpret_cast<uint2 *>(p) = w;
+}
+__device__ __forceinline__ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 // row [width] float32 in shared memory -> out = row / sqrt(mean over the element's group + eps) * (offset + w).
 // Every thread of the CTA must call it.
 template <typename T>
@@ -50,6 +68,15 @@ __device__ __forceinline__ void group_norm_store(const float *row, int width, in
         if (threadIdx.x == 0) inv_s[g] = 1.0f / sqrtf(tot / static_cast<float>(gw) + eps);
     }
     __syncthreads();
+    if (gw % 4 == 0 && aligned16(out) && aligned16(w)) {
+        for (int c = 4 * threadIdx.x; c < width; c += 4 * blockDim.x) {
+            const float inv = inv_s[c / gw];
+            const float4 wv = load4(w + c);
+            store4(out + c, make_float4(row[c] * inv * (offset + wv.x), row[c + 1] * inv * (offset + wv.y), row[c + 2] * inv * (offset + wv.z),
+                                        row[c + 3] * inv * (offset + wv.w)));
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) out[c] = from_f<T>(row[c] * inv_s[c / gw] * (offset + w[c]));
 }
 
@@ -82,15 +109,47 @@ __global__ void __launch_bounds__(kRowThreads) gated_residual_norm_kernel(const 
     const float rs = (y && a.row_scale) ? a.row_scale[t] : 1.f;
     float *x = a.x + t * width;
     T *xc = a.x_cast ? static_cast<T *>(a.x_cast) + t * width : nullptr;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float v = y ? to_f(y[c]) * rs : 0.f;
-        if (eo)
-            for (int k = 0; k < top; ++k) v += to_f(eo[static_cast<int64_t>(a.pair_row[t * top + k]) * width + c]);
-        if (gate) v *= sigmoidf_(to_f(gate[c]) + a.gate_bias[c]);
-        const float xv = x[c] + v;
-        x[c] = xv;
-        row[c] = xv;
-        if (xc) xc[c] = from_f<T>(xv);
+    __shared__ int64_t erow[kMaxTopRows];       // the token's expert rows, read once (not once per channel)
+    if (eo) {
+        for (int k = threadIdx.x; k < top; k += blockDim.x) erow[k] = static_cast<int64_t>(a.pair_row[t * top + k]) * width;
+        __syncthreads();
+    }
+    const bool vec = width % 4 == 0 && aligned16(x) && (!y || (a.ld_y % 4 == 0 && aligned16(y))) &&
+                     (!gate || (a.ld_gate % 4 == 0 && aligned16(gate) && aligned16(a.gate_bias))) && (!eo || aligned16(eo)) &&
+                     (!xc || aligned16(xc));
+    if (vec) {   // the same arithmetic per element, four elements per load
+        for (int c = 4 * threadIdx.x; c < width; c += 4 * blockDim.x) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (y) {
+                const float4 t4 = load4(y + c);
+                v = make_float4(t4.x * rs, t4.y * rs, t4.z * rs, t4.w * rs);
+            }
+            if (eo)
+                for (int k = 0; k < top; ++k) {
+                    const float4 e4 = load4(eo + erow[k] + c);
+                    v.x += e4.x, v.y += e4.y, v.z += e4.z, v.w += e4.w;
+                }
+            if (gate) {
+                const float4 g4 = load4(gate + c), b4 = load4(a.gate_bias + c);
+                v.x *= sigmoidf_(g4.x + b4.x), v.y *= sigmoidf_(g4.y + b4.y), v.z *= sigmoidf_(g4.z + b4.z), v.w *= sigmoidf_(g4.w + b4.w);
+            }
+            const float4 x4 = load4(x + c);
+            const float4 o4 = make_float4(x4.x + v.x, x4.y + v.y, x4.z + v.z, x4.w + v.w);
+            store4(x + c, o4);
+            row[c] = o4.x, row[c + 1] = o4.y, row[c + 2] = o4.z, row[c + 3] = o4.w;
+            if (xc) store4(xc + c, o4);
+        }
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) {
+            float v = y ? to_f(y[c]) * rs : 0.f;
+            if (eo)
+                for (int k = 0; k < top; ++k) v += to_f(eo[erow[k] + c]);
+            if (gate) v *= sigmoidf_(to_f(gate[c]) + a.gate_bias[c]);
+            const float xv = x[c] + v;
+            x[c] = xv;
+            row[c] = xv;
+            if (xc) xc[c] = from_f<T>(xv);
+        }
     }
     if (!a.w_next) return;
     __syncthreads();
@@ -215,7 +274,7 @@ bool hyb_gated_residual_norm(const atoma_gated_residual_args &a_, cudaStream_t s
     if (a.T <= 0) return true;
     if (!hybrid::known_dtype(a.dtype, "atoma_gated_residual_norm")) return false;
     if (a.groups <= 0) a.groups = 1;
-    if (!a.x || a.width <= 0 || (!a.y && !a.expert_out) || (a.expert_out && (!a.pair_row || a.top <= 0)) || (a.gate && !a.gate_bias) ||
+    if (!a.x || a.width <= 0 || (!a.y && !a.expert_out) || (a.expert_out && (!a.pair_row || a.top <= 0 || a.top > kMaxTopRows)) || (a.gate && !a.gate_bias) ||
         (a.w_next && !a.h)) {
         set_status(kErrInvalidArg, "atoma_gated_residual_norm: null or inconsistent arguments");
         return false;

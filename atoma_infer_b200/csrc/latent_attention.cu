@@ -124,12 +124,14 @@ constexpr int kLatKeys = 32;
 constexpr int kLatMaxOut = 32;   // outputs per thread: H * R <= 8192
 
 template <typename T>
-__global__ void __launch_bounds__(kLatThreads) latent_attn_general_kernel(const atoma_latent_attn_args a, int splits,
+__global__ void __launch_bounds__(kLatThreads) latent_attn_general_kernel(const atoma_latent_attn_args a, int splits, int head_chunk,
                                                                           float *__restrict__ partial, float *__restrict__ partial_ml) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
-    const int H = static_cast<int>(a.H), R = static_cast<int>(a.R);
+    // heads [h0, h0 + H) of the a.H heads: a CTA's outputs (H x R) are bounded by its registers, more heads take more CTAs
+    const int h0 = static_cast<int>(blockIdx.z) * head_chunk, H = min(head_chunk, static_cast<int>(a.H) - h0), HT = static_cast<int>(a.H);
+    const int R = static_cast<int>(a.R);
     const int cs = R + 1;                  // padded row of the staged latents
     float *q_s = sm;                       // [H][R]
     float *c_s = q_s + H * R;              // [kLatKeys][R + 1]
@@ -151,12 +153,12 @@ __global__ void __launch_bounds__(kLatThreads) latent_attn_general_kernel(const 
         k_lo = min(p + 1, lo + static_cast<int>(blockIdx.y) * per);
         k_hi = min(p + 1, k_lo + per);
     }
-    const float *q = a.q_lat + static_cast<int64_t>(t) * H * R;
+    const float *q = a.q_lat + (static_cast<int64_t>(t) * HT + h0) * R;
     for (int i = threadIdx.x; i < H * R; i += kLatThreads) q_s[i] = q[i];
     const bool first = blockIdx.y == 0;
     for (int h = threadIdx.x; h < H; h += kLatThreads) {
         const bool snk = first && a.sink != nullptr;
-        m_s[h] = snk ? a.sink[h] : -INFINITY;
+        m_s[h] = snk ? a.sink[h0 + h] : -INFINITY;
         l_s[h] = snk ? 1.f : 0.f;
     }
     float acc[kLatMaxOut];
@@ -219,20 +221,20 @@ __global__ void __launch_bounds__(kLatThreads) latent_attn_general_kernel(const 
         __syncthreads();
     }
     if (partial) {
-        float *o = partial + (static_cast<int64_t>(t) * splits + blockIdx.y) * H * R;
+        float *o = partial + ((static_cast<int64_t>(t) * splits + blockIdx.y) * HT + h0) * R;
 #pragma unroll
         for (int r = 0; r < kLatMaxOut; ++r) {
             const int od = threadIdx.x + r * kLatThreads;
             if (od < H * R) o[od] = acc[r];
         }
-        float *ml = partial_ml + (static_cast<int64_t>(t) * splits + blockIdx.y) * H * 2;
+        float *ml = partial_ml + ((static_cast<int64_t>(t) * splits + blockIdx.y) * HT + h0) * 2;
         for (int h = threadIdx.x; h < H; h += kLatThreads) {
             ml[2 * h] = m_s[h];
             ml[2 * h + 1] = l_s[h];
         }
         return;
     }
-    float *o = a.out + static_cast<int64_t>(t) * H * R;
+    float *o = a.out + (static_cast<int64_t>(t) * HT + h0) * R;
 #pragma unroll
     for (int r = 0; r < kLatMaxOut; ++r) {
         const int od = threadIdx.x + r * kLatThreads;
@@ -256,6 +258,7 @@ __global__ void __launch_bounds__(kLatThreads) latent_attn_general_kernel(const 
 // would multiply mostly masked pairs.
 // ---------------------------------------------------------------------------------------------
 constexpr int kTcKeys = 32;
+constexpr int kSpLd = 40;         // row stride of the partial score tiles (floats)
 constexpr int kTcMaxNT = 8;      // n8 tiles of a warp's share of the latent columns: R <= 64 * warps
 
 template <int MT, int NW>   // row tiles of 16; warps (4 or 8)
@@ -275,8 +278,8 @@ __global__ void __launch_bounds__(32 * NW) latent_attn_tc_kernel(const atoma_lat
     const int ldc = R + 8;
     __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(smraw);                 // [ROWS][R + 8]
     __nv_bfloat16 *Cs = Qs + ROWS * ldc;                                          // [2][32][R + 8]
-    float *Sp = reinterpret_cast<float *>(Cs + 2 * kTcKeys * ldc);                // [4][ROWS][33] partial scores per latent quarter
-    __nv_bfloat16 *Pb = reinterpret_cast<__nv_bfloat16 *>(Sp + 4 * ROWS * 33);    // [ROWS][40]
+    float *Sp = reinterpret_cast<float *>(Cs + 2 * kTcKeys * ldc);                // [4][ROWS][40] partial scores per latent quarter
+    __nv_bfloat16 *Pb = reinterpret_cast<__nv_bfloat16 *>(Sp + 4 * ROWS * kSpLd);  // [ROWS][40]
     float *m_s = reinterpret_cast<float *>(Pb + ROWS * 40);
     float *l_s = m_s + ROWS, *f_s = l_s + ROWS;
     int *p_s = reinterpret_cast<int *>(f_s + ROWS), *lo_s = p_s + ROWS;
@@ -377,16 +380,14 @@ __global__ void __launch_bounds__(32 * NW) latent_attn_tc_kernel(const atoma_lat
                     }
                 }
             }
-            float *sp = Sp + kq * ROWS * 33;
+            float *sp = Sp + kq * ROWS * kSpLd;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int n = 0; n < NKT; ++n) {
-                    float *s0 = sp + (mt * 16 + g) * 33 + key0 + n * 8 + 2 * t4;
-                    s0[0] = sc[mt][n][0];
-                    s0[1] = sc[mt][n][1];
-                    s0[8 * 33] = sc[mt][n][2];
-                    s0[8 * 33 + 1] = sc[mt][n][3];
+                for (int n = 0; n < NKT; ++n) {   // 8-byte stores, row stride 40 floats: a half-warp's stores fall on distinct banks
+                    float *s0 = sp + (mt * 16 + g) * kSpLd + key0 + n * 8 + 2 * t4;
+                    *reinterpret_cast<float2 *>(s0) = make_float2(sc[mt][n][0], sc[mt][n][1]);
+                    *reinterpret_cast<float2 *>(s0 + 8 * kSpLd) = make_float2(sc[mt][n][2], sc[mt][n][3]);
                 }
         }
         __syncthreads();
@@ -394,7 +395,7 @@ __global__ void __launch_bounds__(32 * NW) latent_attn_tc_kernel(const atoma_lat
         for (int r = warp; r < ROWS; r += NW) {
             const int j = j0 + lane;
             const bool vis = j < k_hi && j >= lo_s[r] && j <= p_s[r];
-            const float raw = (Sp[r * 33 + lane] + Sp[(ROWS + r) * 33 + lane]) + (Sp[(2 * ROWS + r) * 33 + lane] + Sp[(3 * ROWS + r) * 33 + lane]);
+            const float raw = (Sp[r * kSpLd + lane] + Sp[(ROWS + r) * kSpLd + lane]) + (Sp[(2 * ROWS + r) * kSpLd + lane] + Sp[(3 * ROWS + r) * kSpLd + lane]);
             const float s = vis ? raw * a.scale : -INFINITY;
             float mx = s;
 #pragma unroll
@@ -483,7 +484,7 @@ __global__ void __launch_bounds__(32 * NW) latent_attn_tc_kernel(const atoma_lat
 
 size_t tc_attn_smem(int mt, int64_t R) {
     const size_t rows = 16 * mt, ldc = R + 8;
-    return rows * ldc * 2 + 2 * kTcKeys * ldc * 2 + 4 * rows * 33 * 4 + rows * 40 * 2 + rows * 5 * 4;
+    return rows * ldc * 2 + 2 * kTcKeys * ldc * 2 + 4 * rows * kSpLd * 4 + rows * 40 * 2 + rows * 5 * 4;
 }
 
 // Splits of one (query, head) are merged in split order: M = max m_k, out = sum_k acc_k e^(m_k - M) / sum_k l_k e^(m_k - M).
@@ -646,12 +647,14 @@ bool hyb_latent_attention(const atoma_latent_attn_args &a, cudaStream_t stream) 
     bool taken = false;
     const bool ok = hyb_latent_attention_tc(a, stream, &taken);
     if (taken || !ok) return ok;
-    if (a.H * a.R > kLatThreads * kLatMaxOut) {
-        set_status(kErrUnsupported, "atoma_latent_attention_paged: heads * latent size = %lld exceeds %d", static_cast<long long>(a.H * a.R),
+    if (a.R > kLatThreads * kLatMaxOut) {
+        set_status(kErrUnsupported, "atoma_latent_attention_paged: a latent size of %lld exceeds %d", static_cast<long long>(a.R),
                    kLatThreads * kLatMaxOut);
         return false;
     }
-    const size_t smem = static_cast<size_t>(a.H * a.R + kLatKeys * (a.R + 1) + a.H * kLatKeys + 3 * a.H) * 4;
+    const int head_chunk = static_cast<int>(std::min<int64_t>(a.H, kLatThreads * kLatMaxOut / a.R));
+    const unsigned head_chunks = static_cast<unsigned>((a.H + head_chunk - 1) / head_chunk);
+    const size_t smem = static_cast<size_t>(head_chunk * a.R + kLatKeys * (a.R + 1) + head_chunk * kLatKeys + 3 * head_chunk) * 4;
     if (smem > 200 * 1024) {
         set_status(kErrUnsupported, "atoma_latent_attention_paged: %zu bytes of shared memory", smem);
         return false;
@@ -675,8 +678,8 @@ bool hyb_latent_attention(const atoma_latent_attn_args &a, cudaStream_t stream) 
         if (!partial) return false;
         partial_ml = partial + n_acc;
     }
-    const dim3 grid(static_cast<unsigned>(a.T), static_cast<unsigned>(splits));
-#define CALL(TT) launch_ex(latent_attn_general_kernel<TT>, grid, dim3(kLatThreads), smem, stream, a, splits, partial, partial_ml)
+    const dim3 grid(static_cast<unsigned>(a.T), static_cast<unsigned>(splits), head_chunks);
+#define CALL(TT) launch_ex(latent_attn_general_kernel<TT>, grid, dim3(kLatThreads), smem, stream, a, splits, head_chunk, partial, partial_ml)
     if (!hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "latent_attn_general_kernel")) return false;
 #undef CALL
     if (splits == 1) return true;

@@ -1,6 +1,6 @@
 // Mixture-of-experts feed-forward on a mixed batch — include/atoma_hybrid.h.
 //
-// Router in float32 (one CTA per token: dot products, the score function, the `top` largest), then the routed
+// Router in float32 (logits in an order that does not depend on the batch, the score function, the `top` largest), then the routed
 // experts without a host read: the (token, k) pairs are sorted by expert on the device into segments padded to
 // whole row tiles, the pairs' input rows are gathered (scaled by the router's weight when the design scales the
 // expert's input), and two grouped products run over the row tiles — gate/up with the clamped gated activation in
@@ -28,39 +28,78 @@ static_assert(kTileRows == tc::kTM, "the experts' segments are padded to the ten
 constexpr int kMaxExperts = 1024;
 
 // ---------------------------------------------------------------------------------------------
-// router
+// router: float32 logits, then the `top` largest per token
+// A warp owns TT tokens x ET router rows (the shared expert's gate row rides as row `experts`).  Whatever the tile shape, a
+// (token, row) logit is summed in ONE order — lane l adds k = l, l + 32, ... in ascending order, then the lanes fold in
+// an xor tree — so a token's logits are bit-identical in a decode step and in a prompt's portion.
 // ---------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T *__restrict__ h, const float *__restrict__ w_router,
-                                                        const float *__restrict__ w_row_gate, int32_t *__restrict__ top_expert,
-                                                        float *__restrict__ top_weight, float *__restrict__ row_gate, int width,
-                                                        int experts, int top, int renormalize) {
-    __shared__ float z_s[kMaxExperts + 1];
+template <typename T, int TT, int ET>
+__global__ void __launch_bounds__(128) moe_logits_kernel(const T *__restrict__ h, const float *__restrict__ w_router,
+                                                         const float *__restrict__ w_row_gate, float *__restrict__ z, int tokens, int width,
+                                                         int experts, int rows) {
     pdl_launch_dependents();
     pdl_wait();
-    const int64_t t = blockIdx.x;
-    const T *hr = h + t * width;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
-    const int rows = experts + (w_row_gate ? 1 : 0);
-    for (int e = warp; e < rows; e += nwarp) {
-        const float *wr = e < experts ? w_router + static_cast<int64_t>(e) * width : w_row_gate;
-        float dot = 0.f;
-        for (int c = lane; c < width; c += 32) dot = fmaf(to_f(hr[c]), wr[c], dot);
+    const int lane = threadIdx.x & 31;
+    const int n_eg = (rows + ET - 1) / ET;
+    const int64_t wid = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    const int t0 = static_cast<int>(wid / n_eg) * TT, e0 = static_cast<int>(wid % n_eg) * ET;
+    if (t0 >= tokens) return;
+    const T *hp[TT];
+    const float *wp[ET];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if (lane == 0) z_s[e] = dot;
+    for (int i = 0; i < TT; ++i) hp[i] = t0 + i < tokens ? h + static_cast<int64_t>(t0 + i) * width : nullptr;
+#pragma unroll
+    for (int j = 0; j < ET; ++j) {
+        const int e = e0 + j;
+        wp[j] = e < experts ? w_router + static_cast<int64_t>(e) * width : (e == experts && e < rows ? w_row_gate : nullptr);
     }
-    __syncthreads();
-    if (warp != 0) return;
-    if (w_row_gate && lane == 0) row_gate[t] = sigmoidf_(z_s[experts]);
+    float acc[TT][ET];
+#pragma unroll
+    for (int i = 0; i < TT; ++i)
+#pragma unroll
+        for (int j = 0; j < ET; ++j) acc[i][j] = 0.f;
+    for (int k = lane; k < width; k += 32) {
+        float hv[TT], wv[ET];
+#pragma unroll
+        for (int i = 0; i < TT; ++i) hv[i] = hp[i] ? to_f(hp[i][k]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < ET; ++j) wv[j] = wp[j] ? wp[j][k] : 0.f;
+#pragma unroll
+        for (int i = 0; i < TT; ++i)
+#pragma unroll
+            for (int j = 0; j < ET; ++j) acc[i][j] = fmaf(hv[i], wv[j], acc[i][j]);
+    }
+#pragma unroll
+    for (int i = 0; i < TT; ++i)
+#pragma unroll
+        for (int j = 0; j < ET; ++j) {
+            float v = acc[i][j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && hp[i] && wp[j]) z[static_cast<int64_t>(t0 + i) * rows + e0 + j] = v;
+        }
+}
+
+// One warp per token: `top` rounds of arg-max over the logits (ties: the lower index), scores = sigmoid(logit).
+__global__ void __launch_bounds__(128) moe_topk_kernel(const float *__restrict__ z, int32_t *__restrict__ top_expert,
+                                                       float *__restrict__ top_weight, float *__restrict__ row_gate, int tokens, int experts,
+                                                       int rows, int top, int renormalize) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+    if (t >= tokens) return;
+    const float *zr = z + t * rows;
+    if (rows > experts && lane == 0) row_gate[t] = sigmoidf_(zr[experts]);
+    uint32_t taken = 0;          // bit i: expert lane + 32 i is already chosen
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int idx = 0x7fffffff;
-        for (int e = lane; e < experts; e += 32) {
-            const float z = z_s[e];
-            if (z > best) {   // ascending e: the lower index wins a tie
-                best = z;
+        for (int e = lane, i = 0; e < experts; e += 32, ++i) {
+            const float v = zr[e];
+            if (!((taken >> i) & 1u) && v > best) {   // ascending e: the lower index wins a tie
+                best = v;
                 idx = e;
             }
         }
@@ -73,15 +112,15 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T *__restrict__ h,
                 idx = oi;
             }
         }
+        if (idx != 0x7fffffff && (idx & 31) == lane) taken |= 1u << (idx >> 5);
         const float s = sigmoidf_(best);
         total += s;
         if (lane == 0) {
-            top_expert[t * top + k] = idx;
+            top_expert[t * top + k] = idx == 0x7fffffff ? 0 : idx;
             top_weight[t * top + k] = s;
-            z_s[idx] = -INFINITY;   // taken
         }
-        __syncwarp();
     }
+    __syncwarp();
     if (renormalize && lane == 0)
         for (int k = 0; k < top; ++k) top_weight[t * top + k] /= total;
 }
@@ -263,11 +302,30 @@ bool hyb_moe_route(const void *h, const float *w_router, const float *w_row_gate
                    static_cast<long long>(top), static_cast<long long>(experts), kMaxExperts);
         return false;
     }
-#define CALL(TT) launch_ex(moe_route_kernel<TT>, dim3(static_cast<unsigned>(T)), dim3(128), 0, stream, static_cast<const TT *>(h), w_router, \
-                           w_row_gate, top_expert, top_weight, row_gate, static_cast<int>(width), static_cast<int>(experts), \
-                           static_cast<int>(top), static_cast<int>(renormalize))
-    return hybrid::launched(HYB_DISPATCH(dtype, CALL), "moe_route_kernel");
+    const int rows = static_cast<int>(experts) + (w_row_gate ? 1 : 0);
+    float *z = static_cast<float *>(get_workspace(stream, static_cast<size_t>(T) * rows * 4, kWorkspaceMoeRoute));
+    if (!z) return false;
+    cudaError_t e;
+    if (T >= 256) {   // prompt portions: 4 x 4 (token, row) pairs per warp share their loads
+        const int64_t warps = ((T + 3) / 4) * ((rows + 3) / 4);
+#define CALL(TT) launch_ex(moe_logits_kernel<TT, 4, 4>, dim3(static_cast<unsigned>((warps + 3) / 4)), dim3(128), 0, stream, \
+                           static_cast<const TT *>(h), w_router, w_row_gate, z, static_cast<int>(T), static_cast<int>(width), \
+                           static_cast<int>(experts), rows)
+        e = HYB_DISPATCH(dtype, CALL);
 #undef CALL
+    } else {          // decode steps: one pair per warp fills the device
+        const int64_t warps = T * rows;
+#define CALL(TT) launch_ex(moe_logits_kernel<TT, 1, 1>, dim3(static_cast<unsigned>((warps + 3) / 4)), dim3(128), 0, stream, \
+                           static_cast<const TT *>(h), w_router, w_row_gate, z, static_cast<int>(T), static_cast<int>(width), \
+                           static_cast<int>(experts), rows)
+        e = HYB_DISPATCH(dtype, CALL);
+#undef CALL
+    }
+    if (!hybrid::launched(e, "moe_logits_kernel")) return false;
+    return hybrid::launched(launch_ex(moe_topk_kernel, dim3(static_cast<unsigned>((T + 3) / 4)), dim3(128), 0, stream,
+                                      static_cast<const float *>(z), top_expert, top_weight, row_gate, static_cast<int>(T),
+                                      static_cast<int>(experts), rows, static_cast<int>(top), static_cast<int>(renormalize)),
+                            "moe_topk_kernel");
 }
 
 int64_t hyb_moe_workspace_bytes(int64_t T, int64_t top, int64_t experts, int64_t width, int64_t ff, uint32_t dtype) {

@@ -233,7 +233,7 @@ def uses_tensor_cores(dtype, R, general):
 @pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("general", [False, True])
 @pytest.mark.parametrize("H,R,window,sink", [(3, 16, 20, True), (1, 40, 0, True), (6, 24, 7, False), (4, 64, 33, True), (2, 8, 1, True),
-                                             (5, 128, 20, True), (16, 64, 0, False), (3, 512, 50, True), (20, 192, 9, True)])
+                                             (5, 128, 20, True), (16, 64, 0, False), (3, 512, 50, True), (20, 192, 9, True), (40, 256, 30, True), (9, 1024, 12, True)])
 def test_latent_attention_on_a_mixed_batch(dtype, general, H, R, window, sink):
     g = torch.Generator().manual_seed(7)
     seqs = [(0, 45), (37, 1), (16, 2), (90, 1), (0, 1), (15, 17)]
