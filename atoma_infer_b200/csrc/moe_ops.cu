@@ -18,6 +18,11 @@
 namespace atoma {
 
 extern int g_hybrid_debug;
+int hyb_moe_umma_tile_rows();
+bool hyb_moe_umma_ok(const void *x, const void *w, const void *out, int64_t K, int64_t ldo);
+bool hyb_moe_grouped_umma(const void *x, const void *w, void *out, int64_t max_tiles, int64_t experts, int64_t N, int64_t K, bool glu,
+                          const int32_t *tile_expert, const int32_t *meta, const int32_t *row_pair, const float *out_weight, float limit,
+                          float alpha, float shift, int *error, cudaStream_t stream);
 
 namespace {
 
@@ -127,11 +132,11 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float *__restrict__
 
 // ---------------------------------------------------------------------------------------------
 // pairs -> expert segments (one CTA)
-// meta[0] = row tiles in use, meta[1] = rows in use (padded)
+// meta[0] = row tiles in use, meta[1] = rows in use (padded), meta[2] = error word of the grouped products (reset here)
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t *__restrict__ top_expert, int32_t *__restrict__ pair_row,
                                                         int32_t *__restrict__ row_pair, int32_t *__restrict__ tile_expert,
-                                                        int32_t *__restrict__ meta, int pairs, int experts, int max_rows) {
+                                                        int32_t *__restrict__ meta, int pairs, int experts, int max_rows, int tile_rows) {
     __shared__ int count[kMaxExperts], base[kMaxExperts];
     pdl_launch_dependents();
     pdl_wait();
@@ -147,13 +152,14 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int32_t *__restric
         int row = 0;
         for (int e = 0; e < experts; ++e) {
             base[e] = row;
-            const int tiles = (count[e] + kTileRows - 1) / kTileRows;
-            for (int i = 0; i < tiles; ++i) tile_expert[row / kTileRows + i] = e;
-            row += tiles * kTileRows;
+            const int tiles = (count[e] + tile_rows - 1) / tile_rows;
+            for (int i = 0; i < tiles; ++i) tile_expert[row / tile_rows + i] = e;
+            row += tiles * tile_rows;
             count[e] = 0;   // reused as the segment's cursor
         }
-        meta[0] = row / kTileRows;
+        meta[0] = row / tile_rows;
         meta[1] = row;
+        meta[2] = 0;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
@@ -264,12 +270,12 @@ struct MoeSpace {
     int64_t max_tiles, max_rows, total;
 };
 
-MoeSpace carve(int64_t T, int64_t top, int64_t experts, int64_t width, int64_t ff, uint32_t dtype, void *base) {
+MoeSpace carve(int64_t T, int64_t top, int64_t experts, int64_t width, int64_t ff, uint32_t dtype, void *base, int64_t tile_rows = kTileRows) {
     const int64_t es = dtype == ATOMA_DTYPE_F32 ? 4 : 2;
     MoeSpace s{};
     const int64_t pairs = T * top;
-    s.max_tiles = std::min<int64_t>((pairs + kTileRows - 1) / kTileRows + experts, pairs);   // every tile in use holds a pair
-    s.max_rows = s.max_tiles * kTileRows;
+    s.max_tiles = std::min<int64_t>((pairs + tile_rows - 1) / tile_rows + experts, pairs);   // every tile in use holds a pair
+    s.max_rows = s.max_tiles * tile_rows;
     int64_t off = 0;
     char *b = static_cast<char *>(base);
     auto take = [&](int64_t bytes) {
@@ -330,7 +336,9 @@ bool hyb_moe_route(const void *h, const float *w_router, const float *w_row_gate
 
 int64_t hyb_moe_workspace_bytes(int64_t T, int64_t top, int64_t experts, int64_t width, int64_t ff, uint32_t dtype) {
     if (T < 0 || top <= 0 || experts <= 0 || width <= 0 || ff <= 0) return -1;
-    return carve(std::max<int64_t>(T, 1), top, experts, width, ff, dtype, nullptr).total;
+    const int64_t t = std::max<int64_t>(T, 1);   // either tile size may be chosen at run time
+    return std::max(carve(t, top, experts, width, ff, dtype, nullptr).total,
+                    carve(t, top, experts, width, ff, dtype, nullptr, hyb_moe_umma_tile_rows()).total);
 }
 
 bool hyb_moe_experts(const atoma_moe_args &a, const void **expert_out, const int32_t **pair_row, cudaStream_t stream) {
@@ -341,7 +349,12 @@ bool hyb_moe_experts(const atoma_moe_args &a, const void **expert_out, const int
         set_status(kErrInvalidArg, "atoma_moe_experts: null argument or empty shape");
         return false;
     }
-    const MoeSpace s = carve(a.T, a.top, a.experts, a.width, a.ff, a.dtype, a.workspace);
+    // prompt-sized steps in bfloat16: 128-row tiles on tcgen05; decode-sized steps: 64-row tiles on the warp-level path
+    const bool umma = a.dtype == ATOMA_DTYPE_BF16 && !(g_hybrid_debug & 1) && (a.T * a.top >= 1024 || (g_hybrid_debug & 8)) &&
+                      a.width >= 64 && a.ff >= 64 && hyb_moe_umma_ok(a.workspace, a.w_gate_up, a.workspace, a.width, a.ff) &&
+                      hyb_moe_umma_ok(a.workspace, a.w_down, a.workspace, a.ff, a.width);
+    const int64_t tile_rows = umma ? hyb_moe_umma_tile_rows() : kTileRows;
+    const MoeSpace s = carve(a.T, a.top, a.experts, a.width, a.ff, a.dtype, a.workspace, tile_rows);
     if (s.total > a.workspace_bytes) {
         set_status(kErrInvalidArg, "atoma_moe_experts: workspace of %lld bytes, %lld needed", static_cast<long long>(a.workspace_bytes),
                    static_cast<long long>(s.total));
@@ -349,7 +362,7 @@ bool hyb_moe_experts(const atoma_moe_args &a, const void **expert_out, const int
     }
     const int pairs = static_cast<int>(a.T * a.top);
     if (!hybrid::launched(launch_ex(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, a.top_expert, s.pair_row, s.row_pair, s.tile_expert,
-                                    s.meta, pairs, static_cast<int>(a.experts), static_cast<int>(s.max_rows)),
+                                    s.meta, pairs, static_cast<int>(a.experts), static_cast<int>(s.max_rows), static_cast<int>(tile_rows)),
                           "moe_sort_kernel"))
         return false;
 #define CALL(TT) launch_ex(moe_gather_kernel<TT>, dim3(static_cast<unsigned>(s.max_rows)), dim3(128), 0, stream, static_cast<const TT *>(a.h), \
@@ -358,7 +371,18 @@ bool hyb_moe_experts(const atoma_moe_args &a, const void **expert_out, const int
     if (!hybrid::launched(HYB_DISPATCH(a.dtype, CALL), "moe_gather_kernel")) return false;
 #undef CALL
     const float *ow = a.scale_input ? nullptr : a.top_weight;
-    if (a.dtype == ATOMA_DTYPE_BF16 && !(g_hybrid_debug & 1)) {   // tensor cores
+    if (umma) {
+        if (!hyb_moe_grouped_umma(s.xs, a.w_gate_up, s.act, s.max_tiles, a.experts, a.ff, a.width, true, s.tile_expert, s.meta, s.row_pair,
+                                  nullptr, a.limit, a.alpha, a.up_shift, s.meta + 2, stream))
+            return false;
+        if (!hyb_moe_grouped_umma(s.act, a.w_down, s.y, s.max_tiles, a.experts, a.width, a.ff, false, s.tile_expert, s.meta, s.row_pair, ow,
+                                  0.f, 0.f, 0.f, s.meta + 2, stream))
+            return false;
+        if (expert_out) *expert_out = s.y;
+        if (pair_row) *pair_row = s.pair_row;
+        return true;
+    }
+    if (a.dtype == ATOMA_DTYPE_BF16 && !(g_hybrid_debug & 1)) {   // warp-level tensor cores
         tc::GemmArgs p{};
         p.a = s.xs, p.lda = a.width;
         p.b = static_cast<const __nv_bfloat16 *>(a.w_gate_up), p.b_zs = 2 * a.ff * a.width, p.b_ks = 1, p.b_ns = a.width;

@@ -30,7 +30,8 @@ def _check():
 
 
 def debug_flags(flags: int) -> None:
-    """bit 0: plain float32 GEMM everywhere; bit 1: general attention kernel only; bit 2: sequential minGRU scan."""
+    """bit 0: plain float32 GEMM everywhere; bit 1: general attention kernel only; bit 2: sequential minGRU scan;
+    bit 3: the routed experts' tcgen05 products for steps of any size."""
     _lib.lib().atoma_debug_hybrid(int(flags))
 
 

@@ -340,7 +340,8 @@ int64_t atoma_hybrid_scratch_bytes(const atoma_hybrid_model *model, int64_t num_
 void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_hybrid_batch *batch, atoma_stream_t stream);
 
 /* Diagnostics: bit 0 = every projection through the plain float32-FMA kernel; bit 1 = the general attention kernel
- * for every batch (no tensor-core prefill / split decode kernels); bit 2 = the sequential minGRU scan. */
+ * for every batch (no tensor-core prefill / split decode kernels); bit 2 = the sequential minGRU scan; bit 3 = the routed
+ * experts' tensor-memory (tcgen05) products for steps of any size (they normally serve steps of 1024 pairs and more). */
 void atoma_debug_hybrid(int flags);
 
 #ifdef __cplusplus

@@ -330,15 +330,24 @@ def test_router_scores_and_choice(dtype, E, top):
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("T,E,top,W,ff", [(7, 5, 2, 48, 24), (150, 3, 1, 40, 70), (33, 12, 3, 50, 9), (1, 4, 4, 64, 64)])
-def test_routed_experts_scale_their_input(dtype, T, E, top, W, ff):
+@pytest.mark.parametrize("T,E,top,W,ff,force_tmem", [(7, 5, 2, 48, 24, False), (150, 3, 1, 40, 70, False), (33, 12, 3, 50, 9, False),
+                                                     (1, 4, 4, 64, 64, False), (1, 4, 4, 64, 64, True), (300, 4, 2, 128, 192, True),
+                                                     (70, 6, 3, 72, 200, True), (700, 8, 2, 256, 136, False)])
+def test_routed_experts_scale_their_input(dtype, T, E, top, W, ff, force_tmem):
+    """bfloat16 steps of 1024 (token, expert) pairs and more run the tensor-memory products on 128-row tiles (forced for smaller
+    steps by debug flag 8), smaller ones the warp-level products on 64-row tiles; float32 the plain kernel."""
     g = torch.Generator().manual_seed(11)
     h = bf(torch.randn(T, W, generator=g))
     wgu, wd = bf(torch.randn(E, 2 * ff, W, generator=g) * 2 / math.sqrt(W)), bf(torch.randn(E, W, ff, generator=g) / math.sqrt(ff))
     idx = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
     if T > 100:
-        idx[:90] = 1                 # one crowded expert (more than one row tile), one that nobody chose
+        idx[:90] = torch.arange(1, 1 + top) % E      # crowded experts (more than one row tile) and, for E = 3, one that nobody chose
+        if E == 3:
+            idx[:] = 1
+            idx[::7] = 2
     wgt = torch.rand(T, top, generator=g) + 0.2
+    if force_tmem:
+        _ops().debug_flags(8)
     got = _ops().moe_experts(h.to(dtype).to(DEV), idx.to(DEV), wgt.to(DEV), wgu.to(dtype).to(DEV), wd.to(dtype).to(DEV), 1.5, 1.702, 1.0)
     want = torch.zeros(T, W, dtype=F64)
     for t in range(T):
