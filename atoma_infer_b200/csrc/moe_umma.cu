@@ -1,10 +1,11 @@
 // Grouped expert products on the 5th-generation tensor cores, for prompt-sized expert segments:
 //   out[row, n] = sum_k x[row, k] w[expert(row tile)][n, k]        (x: the gathered, sorted rows; 128-row tiles per expert)
-// A CTA owns one (row tile, 128-column tile).  Warp 0 streams the operands with TMA (128-byte swizzle, a four-stage mbarrier
+// A CTA owns one (row tile, 128-column tile; 64 gate + 64 up columns with GLU); two CTAs share an SM, so that one's
+// epilogue overlaps the other's main loop.  Warp 0 streams the operands with TMA (128-byte swizzle, a three-stage mbarrier
 // ring; the weight tile's row coordinate is the expert's offset in the stacked weight tensor, read from the device-side
 // tile map), warp 1 issues tcgen05.mma kind::f16 M = 128 with the accumulator in tensor memory, warps 2-5 read it back
 // (tcgen05.ld, thread = row) and apply the epilogue.  With GLU the gate rows and the up rows of the same 128 columns are
-// loaded into one 256-row operand, one MMA of N = 256 makes both products, and the epilogue stores the clamped gated
+// loaded into one 128-row operand, one MMA of N = 128 makes both products, and the epilogue stores the clamped gated
 // activation.  Every wait is bounded: on a timeout the role sets the error word and the CTA still frees its tensor memory.
 #include "common.cuh"
 #include "hybrid_common.cuh"
@@ -16,7 +17,8 @@ namespace {
 
 using namespace hybrid;
 
-constexpr int kUM = 128, kUN = 128, kUK = 64, kUStages = 4, kUThreads = 192;
+constexpr int kUM = 128, kUK = 64, kUStages = 3, kUThreads = 192;
+constexpr int kBRows = 128;          // rows of the weight operand per stage = accumulator columns
 constexpr uint32_t kWaitLimit = 1u << 22;   // try_wait calls (each may block for a hardware time slice) before a role gives up
 
 struct UmmaArgs {
@@ -38,11 +40,12 @@ __device__ __forceinline__ bool wait_bounded(uint64_t *bar, uint32_t parity, int
 }
 
 template <bool GLU>
-__global__ void __launch_bounds__(kUThreads, 1)
+__global__ void __launch_bounds__(kUThreads, 2)
 grouped_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const UmmaArgs p) {
-    constexpr int BROWS = GLU ? 2 * kUN : kUN;
+    constexpr int kUN = GLU ? kBRows / 2 : kBRows;     // output columns of the CTA
+    constexpr int BROWS = kBRows;
     constexpr uint32_t kABytes = kUM * kUK * 2, kBBytes = BROWS * kUK * 2, kStageBytes = kABytes + kBBytes;
-    constexpr uint32_t kTmemCols = GLU ? 256 : 128;
+    constexpr uint32_t kTmemCols = kBRows;
     extern __shared__ unsigned char smem_dyn[];
     unsigned char *tiles = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
     __shared__ __align__(8) uint64_t full[kUStages], empty[kUStages], acc_full;
@@ -195,7 +198,7 @@ bool hyb_moe_grouped_umma(const void *x, const void *w, void *out, int64_t max_t
                           float alpha, float shift, int *error, cudaStream_t stream) {
     CUtensorMap map_x, map_w;
     const int64_t rpe = glu ? 2 * N : N;
-    if (!encode_2d(&map_x, x, max_tiles * kUM, K, kUM) || !encode_2d(&map_w, w, experts * rpe, K, kUN)) return false;
+    if (!encode_2d(&map_x, x, max_tiles * kUM, K, kUM) || !encode_2d(&map_w, w, experts * rpe, K, glu ? kBRows / 2 : kBRows)) return false;
     UmmaArgs a{};
     a.out = static_cast<__nv_bfloat16 *>(out);
     a.ldo = N;
@@ -210,14 +213,14 @@ bool hyb_moe_grouped_umma(const void *x, const void *w, void *out, int64_t max_t
     a.alpha = alpha;
     a.shift = shift;
     a.error = error;
-    const dim3 grid(static_cast<unsigned>((N + kUN - 1) / kUN), static_cast<unsigned>(max_tiles));
+    const int un = glu ? kBRows / 2 : kBRows;
+    const dim3 grid(static_cast<unsigned>((N + un - 1) / un), static_cast<unsigned>(max_tiles));
+    const size_t smem = kUStages * (kUM * kUK * 2 + kBRows * kUK * 2) + 1024;
     cudaError_t e;
     if (glu) {
-        const size_t smem = kUStages * (kUM * kUK * 2 + 2 * kUN * kUK * 2) + 1024;
         cudaFuncSetAttribute(grouped_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         e = launch_ex(grouped_umma_kernel<true>, grid, dim3(kUThreads), smem, stream, map_x, map_w, a);
     } else {
-        const size_t smem = kUStages * (kUM * kUK * 2 + kUN * kUK * 2) + 1024;
         cudaFuncSetAttribute(grouped_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         e = launch_ex(grouped_umma_kernel<false>, grid, dim3(kUThreads), smem, stream, map_x, map_w, a);
     }
