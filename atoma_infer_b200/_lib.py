@@ -207,7 +207,16 @@ class LatentAttnArgs(C.Structure):
 
     _fields_ = ([(n, C.c_void_p) for n in ("q_lat", "latent_cache", "out", "positions", "token_seq", "query_start", "block_tables", "sink")] +
                 [(n, C.c_int64) for n in ("T", "B", "max_blocks", "H", "R", "block_size", "window")] +
-                [("scale", C.c_float), ("dtype", C.c_uint32), ("max_query_len", C.c_int32), ("max_seq_len", C.c_int32)])
+                [("scale", C.c_float), ("dtype", C.c_uint32), ("max_query_len", C.c_int32), ("max_seq_len", C.c_int32),
+                 ("skip_min_q", C.c_int32)])
+
+
+class LatentExpandedArgs(C.Structure):
+    """struct atoma_latent_expanded_args"""
+
+    _fields_ = ([(n, C.c_void_p) for n in ("q", "latent_cache", "w_uk", "w_uv", "out", "query_start", "context_lens", "block_tables", "sink")] +
+                [(n, C.c_int64) for n in ("T", "B", "max_blocks", "H", "dim", "R", "block_size", "window", "max_keys")] +
+                [("scale", C.c_float), ("min_q", C.c_int32), ("max_query_len", C.c_int32), ("max_seq_len", C.c_int32)])
 
 
 class MoeArgs(C.Structure):
@@ -226,7 +235,8 @@ class HybridBatch(C.Structure):
                 [(n, C.c_void_p) for n in ("tokens", "positions", "slot_mapping", "token_seq", "query_start", "context_lens",
                                            "block_tables", "state_slots", "selected", "scratch")] +
                 [("scratch_bytes", C.c_int64)] +
-                [(n, C.c_void_p) for n in ("logits", "next_tokens", "residual_trace")])
+                [(n, C.c_void_p) for n in ("logits", "next_tokens", "residual_trace")] +
+                [("long_seqs", C.c_int32), ("long_min_q", C.c_int32), ("long_tokens", C.c_int64), ("long_ctx_sum", C.c_int64)])
 
 
 # Exact C parameter lists, in header order.
@@ -340,6 +350,7 @@ SIGNATURES = {
     "atoma_latent_norm_cache": (None, [C.c_void_p, C.c_int64] + [C.c_void_p] * 5 + [C.c_int64] * 3 + [C.c_float, C.c_uint32, C.c_void_p]),
     "atoma_head_project": (None, [C.c_void_p] * 3 + [C.c_int64] * 4 + [C.c_int32, C.c_uint32, C.c_void_p]),
     "atoma_latent_attention_paged": (None, [C.POINTER(LatentAttnArgs), C.c_void_p]),
+    "atoma_latent_attention_expanded": (None, [C.POINTER(LatentExpandedArgs), C.c_void_p]),
     "atoma_moe_route": (None, [C.c_void_p] * 6 + [C.c_int64] * 4 + [C.c_int32, C.c_uint32, C.c_void_p]),
     "atoma_glu_clamped": (None, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_uint32,
                                  C.c_void_p]),

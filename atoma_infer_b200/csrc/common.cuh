@@ -43,7 +43,7 @@ const DeviceInfo &current_device_info();
 // Library-owned scratch, one per (device, stream, tag); grows monotonically, zero-initialised
 // when (re)allocated.  Used for the decode kernel's split partials + arrival counters and for the
 // device copy of a swap mapping.
-enum : int { kWorkspaceDecode = 0, kWorkspaceSwapMap = 1, kWorkspaceGemm = 2, kWorkspaceGemmCounters = 3, kWorkspaceSkinnyTail = 4, kWorkspaceHybridAttn = 5, kWorkspaceMoeRoute = 6, kWorkspaceTags = 7 };
+enum : int { kWorkspaceDecode = 0, kWorkspaceSwapMap = 1, kWorkspaceGemm = 2, kWorkspaceGemmCounters = 3, kWorkspaceSkinnyTail = 4, kWorkspaceHybridAttn = 5, kWorkspaceMoeRoute = 6, kWorkspaceLatentExpand = 7, kWorkspaceTags = 8 };
 void *get_workspace(cudaStream_t stream, size_t bytes, int tag);
 
 // Launch mode (process-wide, atoma_set_launch_mode): programmatic dependent launch between this

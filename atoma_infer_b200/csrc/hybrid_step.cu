@@ -45,6 +45,8 @@ bool hyb_latent_norm_cache(const void *, int64_t, const float *, const float *, 
                            float, uint32_t, cudaStream_t);
 bool hyb_head_project(const void *, const void *, void *, int64_t, int64_t, int64_t, int64_t, int32_t, uint32_t, cudaStream_t);
 bool hyb_latent_attention(const atoma_latent_attn_args &, cudaStream_t);
+bool hyb_latent_expanded_ok(int64_t, int64_t, int64_t, uint32_t);
+bool hyb_latent_attention_expanded(const atoma_latent_expanded_args &, cudaStream_t);
 bool hyb_moe_route(const void *, const float *, const float *, int32_t *, float *, float *, int64_t, int64_t, int64_t, int64_t, int32_t,
                    uint32_t, cudaStream_t);
 int64_t hyb_moe_workspace_bytes(int64_t, int64_t, int64_t, int64_t, int64_t, uint32_t);
@@ -164,7 +166,11 @@ bool prenorm_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, con
                                stream))
         return false;
     if (!hyb_linear(s.cq, l.w_uq, s.q, T, l.heads * l.dim, l.q_rank, dt, stream)) return false;
-    if (!hyb_head_project(s.q, l.w_uk, s.qlat, T, l.heads, l.dim, l.kv_rank, 1, dt, stream)) return false;
+    // long prompt portions run on expanded keys and values (4x fewer multiply-adds per pair at usual sizes); decoded tokens and
+    // short portions run in the latent space (the cache is read once for all heads)
+    const bool expanded = b.long_seqs > 0 && b.long_min_q >= 32 && hyb_latent_expanded_ok(l.dim, l.vdim, l.kv_rank, dt);
+    const bool latent_too = !expanded || b.long_seqs < b.num_seqs;
+    if (latent_too && !hyb_head_project(s.q, l.w_uk, s.qlat, T, l.heads, l.dim, l.kv_rank, 1, dt, stream)) return false;
     atoma_latent_attn_args a{};
     a.q_lat = s.qlat;
     a.latent_cache = l.latent_cache;
@@ -185,8 +191,38 @@ bool prenorm_layer(const atoma_hybrid_model &m, const atoma_hybrid_batch &b, con
     a.dtype = dt;
     a.max_query_len = b.max_query_len;
     a.max_seq_len = b.max_seq_len;
-    if (!hyb_latent_attention(a, stream)) return false;
-    if (!hyb_head_project(s.olat, l.w_uv, s.act, T, l.heads, l.vdim, l.kv_rank, 0, dt, stream)) return false;
+    a.skip_min_q = expanded ? b.long_min_q : 0;
+    if (latent_too) {
+        if (!hyb_latent_attention(a, stream)) return false;
+        if (!hyb_head_project(s.olat, l.w_uv, s.act, T, l.heads, l.vdim, l.kv_rank, 0, dt, stream)) return false;
+    }
+    if (expanded) {   // after the latent path: it rewrites the long sequences' rows of s.act
+        atoma_latent_expanded_args e{};
+        e.q = s.q;
+        e.latent_cache = l.latent_cache;
+        e.w_uk = l.w_uk;
+        e.w_uv = l.w_uv;
+        e.out = s.act;
+        e.query_start = b.query_start;
+        e.context_lens = b.context_lens;
+        e.block_tables = b.block_tables;
+        e.sink = l.sink;
+        e.T = T;
+        e.B = b.num_seqs;
+        e.max_blocks = b.max_blocks;
+        e.H = l.heads;
+        e.dim = l.dim;
+        e.R = l.kv_rank;
+        e.block_size = m.block_size;
+        e.window = l.window;
+        e.max_keys = b.long_tokens + (l.window > 0 ? std::min<int64_t>(b.long_ctx_sum, static_cast<int64_t>(b.long_seqs) * (l.window - 1))
+                                                   : b.long_ctx_sum);
+        e.scale = l.scale;
+        e.min_q = b.long_min_q;
+        e.max_query_len = b.max_query_len;
+        e.max_seq_len = b.max_seq_len;
+        if (!hyb_latent_attention_expanded(e, stream)) return false;
+    }
     if (!hyb_linear(s.act, l.w_o, s.y, T, W, l.heads * l.vdim, dt, stream)) return false;
     const bool side = l.side_gate != nullptr;
     atoma_gated_residual_args r{};
@@ -294,6 +330,7 @@ extern "C" int64_t atoma_hybrid_abi_sizeof(int which) {
         case 4: return sizeof(atoma_gated_residual_args);
         case 5: return sizeof(atoma_latent_attn_args);
         case 6: return sizeof(atoma_moe_args);
+        case 7: return sizeof(atoma_latent_expanded_args);
         default: return -1;
     }
 }

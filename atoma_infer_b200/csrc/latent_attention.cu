@@ -11,15 +11,19 @@
 // tiles that start at the window's first key, so a query's result does not depend on the batch around it.
 #include "common.cuh"
 #include "hybrid_common.cuh"
+#include "mha_params.h"
 #include "tc_products.cuh"
 
 #include "atoma_hybrid.h"
 
 #include <algorithm>
+#include <cstring>
 
 namespace atoma {
 
 extern int g_hybrid_debug;
+int try_launch_prefill_tc(const MhaParams &p, bool is_bf16, cudaStream_t stream);   // prefill_attention.cu
+bool hyb_linear(const void *, const void *, void *, int64_t, int64_t, int64_t, uint32_t, cudaStream_t);
 
 namespace {
 
@@ -141,6 +145,7 @@ __global__ void __launch_bounds__(kLatThreads) latent_attn_general_kernel(const 
     float *f_s = l_s + H;                  // [H] rescale factor of the tile
     const int t = blockIdx.x;
     const int b = a.token_seq[t];
+    if (a.skip_min_q > 0 && a.query_start[b + 1] - a.query_start[b] >= a.skip_min_q) return;   // served on expanded keys
     const int p = static_cast<int>(a.positions[t]);
     const int32_t *bt = a.block_tables + static_cast<int64_t>(b) * a.max_blocks;
     const T *cache = static_cast<const T *>(a.latent_cache);
@@ -275,6 +280,7 @@ __global__ void __launch_bounds__(32 * NW) latent_attn_tc_kernel(const atoma_lat
     const int q0 = a.query_start[b], nq = a.query_start[b + 1] - q0;
     const int row0 = blockIdx.x * ROWS, nrows = nq * H;
     if (row0 >= nrows) return;
+    if (a.skip_min_q > 0 && nq >= a.skip_min_q) return;   // served on expanded keys
     const int ldc = R + 8;
     __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(smraw);                 // [ROWS][R + 8]
     __nv_bfloat16 *Cs = Qs + ROWS * ldc;                                          // [2][32][R + 8]
@@ -520,6 +526,47 @@ __global__ void __launch_bounds__(128) latent_split_reduce_kernel(const float *_
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Long prompt portions on expanded keys and values: plan (which sequences, which keys), gather of their latents.
+// ---------------------------------------------------------------------------------------------
+__global__ void latent_expand_plan_kernel(const int32_t *__restrict__ query_start, const int32_t *__restrict__ context_lens, int B,
+                                          int window, int min_q, int32_t *__restrict__ cu_k, int32_t *__restrict__ key_lo) {
+    pdl_launch_dependents();
+    pdl_wait();
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int acc = 0;
+    for (int b = 0; b < B; ++b) {
+        const int nq = query_start[b + 1] - query_start[b], ctx = context_lens[b];
+        int lo = 0, n = 0;
+        if (nq >= min_q) {
+            lo = window > 0 ? max(0, ctx - window + 1) : 0;   // the first key the portion's first query sees
+            n = ctx + nq - lo;
+        }
+        cu_k[b] = acc;
+        key_lo[b] = lo;
+        acc += n;
+    }
+    cu_k[B] = acc;
+}
+
+// One warp per gathered row: C[cu_k[b] + i, :] = cache[page(key_lo[b] + i), :]
+__global__ void __launch_bounds__(256) latent_gather_kernel(const __nv_bfloat16 *__restrict__ cache, const int32_t *__restrict__ block_tables,
+                                                            int64_t max_blocks, const int32_t *__restrict__ cu_k,
+                                                            const int32_t *__restrict__ key_lo, __nv_bfloat16 *__restrict__ out, int R,
+                                                            int bs) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y;
+    const int n = cu_k[b + 1] - cu_k[b];
+    const int i = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (i >= n) return;
+    const int j = key_lo[b] + i;
+    const int32_t *bt = block_tables + static_cast<int64_t>(b) * max_blocks;
+    const uint4 *src = reinterpret_cast<const uint4 *>(cache + (static_cast<int64_t>(bt[j / bs]) * bs + j % bs) * R);
+    uint4 *dst = reinterpret_cast<uint4 *>(out + static_cast<int64_t>(cu_k[b] + i) * R);
+    for (int c = threadIdx.x & 31; c < R / 8; c += 32) dst[c] = src[c];
+}
+
 }  // namespace
 
 #define HYB_DISPATCH(dtype, CALL) ((dtype) == ATOMA_DTYPE_BF16 ? CALL(__nv_bfloat16) : CALL(float))
@@ -691,6 +738,60 @@ bool hyb_latent_attention(const atoma_latent_attn_args &a, cudaStream_t stream) 
                             "latent_split_reduce_kernel");
 }
 
+
+// Shapes the expanded path takes: bfloat16, equal key and value head sizes of 64 or 128, 16-byte latent rows, sm_100.
+bool hyb_latent_expanded_ok(int64_t dim, int64_t vdim, int64_t R, uint32_t dtype) {
+    return dtype == ATOMA_DTYPE_BF16 && dim == vdim && (dim == 64 || dim == 128) && R % 8 == 0 && current_device_info().cc_major == 10 &&
+           !(g_hybrid_debug & 2);
+}
+
+bool hyb_latent_attention_expanded(const atoma_latent_expanded_args &a, cudaStream_t stream) {
+    if (a.T <= 0 || a.B <= 0 || a.max_keys <= 0) return true;
+    if (!a.q || !a.latent_cache || !a.w_uk || !a.w_uv || !a.out || !a.query_start || !a.context_lens || !a.block_tables || a.H <= 0 ||
+        a.min_q < 32 || !hyb_latent_expanded_ok(a.dim, a.dim, a.R, ATOMA_DTYPE_BF16)) {
+        set_status(kErrInvalidArg, "atoma_latent_attention_expanded: null argument, or a shape outside bfloat16 heads of 64 / 128 with min_q >= 32");
+        return false;
+    }
+    const int64_t HD = a.H * a.dim;
+    auto up = [](int64_t x) { return (x + 255) / 256 * 256; };
+    const int64_t rows = a.max_keys + 128;   // the attention kernel's TMA boxes may start up to a tile before the end
+    const int64_t b_int = up((2 * a.B + 2) * 4), b_c = up(rows * a.R * 2), b_kv = up(rows * HD * 2);
+    char *ws = static_cast<char *>(get_workspace(stream, static_cast<size_t>(b_int + b_c + 2 * b_kv), kWorkspaceLatentExpand));
+    if (!ws) return false;
+    int32_t *cu_k = reinterpret_cast<int32_t *>(ws), *key_lo = cu_k + a.B + 1;
+    __nv_bfloat16 *C = reinterpret_cast<__nv_bfloat16 *>(ws + b_int);
+    __nv_bfloat16 *K = reinterpret_cast<__nv_bfloat16 *>(ws + b_int + b_c), *V = reinterpret_cast<__nv_bfloat16 *>(ws + b_int + b_c + b_kv);
+    if (!hybrid::launched(launch_ex(latent_expand_plan_kernel, dim3(1), dim3(32), 0, stream, a.query_start, a.context_lens,
+                                    static_cast<int>(a.B), static_cast<int>(a.window), static_cast<int>(a.min_q), cu_k, key_lo),
+                          "latent_expand_plan_kernel"))
+        return false;
+    const int64_t span = a.window > 0 ? std::min<int64_t>(a.max_seq_len, a.window - 1 + a.max_query_len) : a.max_seq_len;
+    const dim3 gg(static_cast<unsigned>((span + 7) / 8), static_cast<unsigned>(a.B));
+    if (!hybrid::launched(launch_ex(latent_gather_kernel, gg, dim3(256), 0, stream, static_cast<const __nv_bfloat16 *>(a.latent_cache),
+                                    a.block_tables, a.max_blocks, static_cast<const int32_t *>(cu_k), static_cast<const int32_t *>(key_lo), C,
+                                    static_cast<int>(a.R), static_cast<int>(a.block_size)),
+                          "latent_gather_kernel"))
+        return false;
+    if (!hyb_linear(C, a.w_uk, K, a.max_keys, HD, a.R, ATOMA_DTYPE_BF16, stream)) return false;
+    if (!hyb_linear(C, a.w_uv, V, a.max_keys, HD, a.R, ATOMA_DTYPE_BF16, stream)) return false;
+    MhaParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.q = a.q, p.k = K, p.v = V, p.o = a.out;
+    p.cu_q = a.query_start, p.cu_k = cu_k;
+    p.q_rs = p.k_rs = p.v_rs = p.o_rs = HD;
+    p.q_hs = p.k_hs = p.v_hs = p.o_hs = a.dim;
+    p.b = static_cast<int>(a.B), p.h = p.h_k = static_cast<int>(a.H), p.d = static_cast<int>(a.dim);
+    p.seqlen_q = a.max_query_len, p.seqlen_k = static_cast<int>(span);
+    p.page = 1;
+    p.scale = a.scale, p.scale_log2 = a.scale * 1.4426950408889634f;
+    p.is_causal = 1, p.k_cumulative = 1;
+    p.window_left = static_cast<int>(a.window), p.min_len_q = a.min_q, p.sink = a.sink;
+    const int r = try_launch_prefill_tc(p, true, stream);
+    if (r == 1) return true;
+    if (r == 0) set_status(kErrUnsupported, "atoma_latent_attention_expanded: the step is outside the tensor-memory attention kernel's envelope");
+    return false;
+}
+
 }  // namespace atoma
 
 using namespace atoma;
@@ -706,6 +807,14 @@ extern "C" void atoma_head_project(const void *in, const void *w, void *out, int
                                    uint32_t dtype, atoma_stream_t stream) {
     clear_status();
     hyb_head_project(in, w, out, T, H, n, R, absorb, dtype, static_cast<cudaStream_t>(stream));
+}
+extern "C" void atoma_latent_attention_expanded(const atoma_latent_expanded_args *args, atoma_stream_t stream) {
+    clear_status();
+    if (!args) {
+        set_status(kErrInvalidArg, "atoma_latent_attention_expanded: args is NULL");
+        return;
+    }
+    hyb_latent_attention_expanded(*args, static_cast<cudaStream_t>(stream));
 }
 extern "C" void atoma_latent_attention_paged(const atoma_latent_attn_args *args, atoma_stream_t stream) {
     clear_status();

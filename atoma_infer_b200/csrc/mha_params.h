@@ -32,6 +32,12 @@ struct MhaParams {
     int is_causal;
     int k_cumulative;  // cu_k holds b+1 cumulative offsets (1) or b per-sequence lengths (0)
     int unpadded_lse;
+    // tcgen05 prefill kernel only (zero = off): causal sliding window (query i sees the window_left keys up to its own), a
+    // per-head softmax sink (one more term exp(sink[h]) of the denominator, not scaled), and sequences with fewer than
+    // min_len_q query rows are left alone (nothing is read or written for them)
+    int window_left;
+    int min_len_q;
+    const float *sink;
 };
 
 }  // namespace atoma

@@ -122,13 +122,15 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const PfSeq si = pf_seq(p, bidb);
     const int len_q = si.len_q, len_k = si.len_k;
     const int shift = len_k - len_q;  // mask.h:171-172: key j visible to query i iff j <= i + shift
+    const bool skip = p.min_len_q > 0 && len_q < p.min_len_q;   // the caller serves this sequence elsewhere
+    const int window = (p.is_causal && p.window_left > 0) ? p.window_left : 0;
     // Query tile t of this CTA covers rows m0[t] .. m0[t] + 127 and needs the first nt[t] key tiles.
     int m0[kQTiles], nt[kQTiles];
 #pragma unroll
     for (int t = 0; t < kQTiles; ++t) {
         m0[t] = (m_block * kQTiles + t) * kPfM;
         nt[t] = 0;
-        if (m0[t] < len_q) {
+        if (m0[t] < len_q && !skip) {
             nt[t] = (len_k + kPfN - 1) / kPfN;
             if (p.is_causal) {
                 const int lim = min(m0[t] + kPfM, len_q) + shift;  // one past the last visible key of the tile
@@ -137,6 +139,14 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
     }
     const int n_max = max(nt[0], nt[1]);
+    // Sliding window: the CTA starts at the key tile that holds the lowest key its first row can see (both query tiles
+    // start there: the later one's extra tiles are masked out, which the running softmax takes like any masked tile).
+    // Stage indices and barrier parities below count tiles from n_lo.
+    int n_lo = 0;
+    if (window > 0) {
+        const int first_key = m0[0] + shift - window + 1;
+        n_lo = first_key > 0 ? first_key / kPfN : 0;
+    }
     const int kvh = head / (p.h / p.h_k);  // flash_fwd_kernel.h:593
 
     if (warp < 4) {
@@ -179,9 +189,9 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (nt[t] > 0)
                     load_tile(sq + t * C::kTileBytes, &map_q, &q_full[t], qg, p.q_rs, m0[t], len_q, si.q_row0 + m0[t],
                               head, si.q_batch, kL2EvictFirst);
-            for (int j = 0; j < n_max; ++j) {
-                const int s = j % kKvStages;
-                const uint32_t par = ((j / kKvStages) & 1) ^ 1;
+            for (int j = n_lo; j < n_max; ++j) {
+                const int s = (j - n_lo) % kKvStages;
+                const uint32_t par = (((j - n_lo) / kKvStages) & 1) ^ 1;
                 mbar_wait(&k_empty[s], par);
                 load_tile(sk + s * C::kTileBytes, &map_k, &k_full[s], kg, p.k_rs, j * kPfN, len_k,
                           si.k_row0 + j * kPfN, kvh, si.k_batch, kL2EvictLast);
@@ -202,7 +212,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const uint32_t idesc_qk = umma_idesc_f16(kPfM, kPfN, kBf16, false);
             const uint32_t idesc_pv = umma_idesc_f16(kPfM, D, kBf16, true);
             auto issue_qk = [&](int t, int j) {
-                const int s = j % kKvStages;
+                const int s = (j - n_lo) % kKvStages;
                 const uint32_t q_addr = smem_u32(sq + t * C::kTileBytes);
                 const uint32_t k_addr = smem_u32(sk + s * C::kTileBytes);
                 const uint32_t tmem_s = tmem_base + t * 128;
@@ -218,7 +228,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 __syncwarp();
             };
             auto issue_pv = [&](int t, int j) {
-                const int s = j % kKvStages;
+                const int s = (j - n_lo) % kKvStages;
                 const uint32_t v_addr = smem_u32(sv + s * C::kTileBytes);
                 const uint32_t tmem_p = tmem_base + t * 128;
                 const uint32_t tmem_o = tmem_base + 256 + t * 128;
@@ -227,7 +237,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     for (int kk = 0; kk < kPfN / 16; ++kk) {
                         // 16 keys = 16 rows of 128 bytes of V; 16 P values = 8 packed 32-bit columns
                         umma_f16_ts(tmem_o, tmem_p + kk * 8, umma_desc_mn_sw128(v_addr + kk * 16 * 128, C::kHalfBytes),
-                                    idesc_pv, (j | kk) != 0 ? 1u : 0u);
+                                    idesc_pv, ((j - n_lo) | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit(&pv_done[t]);
                 }
@@ -240,25 +250,26 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (nt[t] > 0) {
                     mbar_wait(&q_full[t], 0);
                     tc_fence_after_sync();
-                    issue_qk(t, 0);
+                    issue_qk(t, n_lo);
                 }
             }
             if (elect_one_sync()) umma_commit(&k_empty[0]);
             __syncwarp();
-            for (int j = 0; j < n_max; ++j) {
-                const int s = j % kKvStages, sn = (j + 1) % kKvStages;
-                mbar_wait(&v_full[s], (j / kKvStages) & 1);
+            for (int j = n_lo; j < n_max; ++j) {
+                const int jj = j - n_lo;
+                const int s = jj % kKvStages, sn = (jj + 1) % kKvStages;
+                mbar_wait(&v_full[s], (jj / kKvStages) & 1);
                 bool k_next_ready = false;
 #pragma unroll
                 for (int t = 0; t < kQTiles; ++t) {
                     if (j < nt[t]) {
-                        mbar_wait(&p_full[t], j & 1);
+                        mbar_wait(&p_full[t], jj & 1);
                         tc_fence_after_sync();
                         issue_pv(t, j);
                     }
                     if (j + 1 < nt[t]) {
                         if (!k_next_ready) {
-                            mbar_wait(&k_full[sn], ((j + 1) / kKvStages) & 1);
+                            mbar_wait(&k_full[sn], ((jj + 1) / kKvStages) & 1);
                             k_next_ready = true;
                         }
                         tc_fence_after_sync();
@@ -293,8 +304,12 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         if (n_tiles > 0) {
             float m_ref = -INFINITY, l_run = 0.f;
-            for (int j = 0; j < n_tiles; ++j) {
-                mbar_wait(&s_full[t], j & 1);
+            if (p.sink) {   // the sink is one more term of the denominator: the running state starts from it
+                m_ref = p.sink[head] * 1.4426950408889634f;
+                l_run = 1.f;
+            }
+            for (int j = n_lo; j < n_tiles; ++j) {
+                mbar_wait(&s_full[t], (j - n_lo) & 1);
                 tc_fence_after_sync();
                 uint32_t sv_[128];
 #pragma unroll
@@ -304,11 +319,13 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const int col0 = j * kPfN;
                 const bool tail = col0 + kPfN > len_k;
                 const bool diag = p.is_causal && (col0 + kPfN - 1 > m0t + shift);
-                if (tail || diag) {
+                const bool low = window > 0 && col0 < m0t + kPfM + shift - window;   // some row's window starts inside or after this tile
+                if (tail || diag || low) {
                     const int lim = p.is_causal ? min(len_k, grow + shift + 1) : len_k;  // first masked column
+                    const int lb = window > 0 ? grow + shift - window + 1 : -(1 << 30);  // first visible column
 #pragma unroll
                     for (int c = 0; c < 128; ++c)
-                        if (col0 + c >= lim) sv_[c] = 0xff800000u;  // -inf
+                        if (col0 + c >= lim || col0 + c < lb) sv_[c] = 0xff800000u;  // -inf
                 }
                 // eight independent chains: a single running max / sum is 128 dependent operations
                 float mx8[8];
@@ -325,10 +342,10 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const float alpha = need ? (m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m_tile)) : 1.f;
                     if (need) m_ref = m_tile;
                     l_run *= alpha;
-                    if (j > 0) {
+                    if (j > n_lo) {
                         // O of this row lives in tensor memory: wait until P.V of the previous tile has
                         // been accumulated, rescale, write back.  Rare after the first tiles.
-                        mbar_wait(&pv_done[t], (j - 1) & 1);
+                        mbar_wait(&pv_done[t], (j - 1 - n_lo) & 1);
                         tc_fence_after_sync();
 #pragma unroll
                         for (int c = 0; c < D / 32; ++c) {
@@ -364,7 +381,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 if (lane == 0) mbar_arrive(&p_full[t]);
             }
             // ---- epilogue: O / rowsum -> global ----
-            mbar_wait(&pv_done[t], (n_tiles - 1) & 1);
+            mbar_wait(&pv_done[t], (n_tiles - 1 - n_lo) & 1);
             tc_fence_after_sync();
             const bool empty = (l_run == 0.f || l_run != l_run);
             const float inv = empty ? 0.f : 1.f / l_run;
@@ -387,7 +404,7 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             if (p.lse && grow < len_q)
                 p.lse[lse_idx] = empty ? INFINITY : m_ref * 0.6931471805599453f + __logf(l_run);
-        } else if (grow < len_q) {
+        } else if (grow < len_q && !skip) {
             // No visible key for any row of this tile: O = 0, LSE = +inf (flash_fwd_kernel.h:543-582).
 #pragma unroll
             for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4 *>(og + c * 8) = make_uint4(0, 0, 0, 0);

@@ -39,6 +39,7 @@ from .scheduler import StepPlan
 from .worker import InputStager, SequenceInput
 
 MIXER_ATTENTION, MIXER_MINGRU, MIXER_LATENT = 0, 1, 2
+LONG_PORTION = 128        # tokens of a sequence in one step from which latent attention runs on expanded keys and values
 BLOCK_STYLES = {"sandwich": 0, "prenorm": 1}
 ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
 DTYPE_CODES = {torch.bfloat16: 1, torch.float32: 2}
@@ -373,6 +374,10 @@ class HybridExecutor:
         hb.num_tokens, hb.num_seqs, hb.num_selected, hb.max_blocks = T, B, S, bt.shape[1]
         hb.max_query_len = max(c.count for c in chunks)
         hb.max_seq_len = max(c.start + c.count for c in chunks)
+        if self.spec.block_style == "prenorm":
+            long_ = [c for c in chunks if c.count >= LONG_PORTION]
+            hb.long_seqs, hb.long_min_q = len(long_), LONG_PORTION
+            hb.long_tokens, hb.long_ctx_sum = sum(c.count for c in long_), sum(c.start for c in long_)
         hb.tokens, hb.positions, hb.slot_mapping = v["tokens"].data_ptr(), v["positions"].data_ptr(), v["slot_mapping"].data_ptr()
         hb.token_seq, hb.query_start, hb.context_lens = tseq.data_ptr(), v["query_start"].data_ptr(), v["context_lengths"].data_ptr()
         hb.block_tables, hb.state_slots = bt.data_ptr(), sslots.data_ptr()

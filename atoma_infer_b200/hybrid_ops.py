@@ -282,3 +282,21 @@ def finish_logits_greedy(logits, scale, softcap):
     _lib.lib().atoma_finish_logits_greedy(_p(logits), _p(out), _p(tok), R, V, scale, softcap, _CODES[logits.dtype], _s())
     _check()
     return out, tok
+
+
+def latent_attention_expanded(q, cache, w_uk, w_uv, query_start, context_lens, block_tables, sink, H, dim, R, block_size, window, scale,
+                              min_q, max_query_len, max_seq_len, max_keys, out=None):
+    """Rows of sequences with at least min_q tokens in the step are written; the others are left as they are in `out`."""
+    from ._lib import LatentExpandedArgs
+    T = q.shape[0]
+    if out is None:
+        out = torch.zeros((T, H * dim), dtype=q.dtype, device=q.device)
+    a = LatentExpandedArgs()
+    a.q, a.latent_cache, a.w_uk, a.w_uv, a.out = _p(q), _p(cache), _p(w_uk), _p(w_uv), _p(out)
+    a.query_start, a.context_lens, a.block_tables, a.sink = _p(query_start), _p(context_lens), _p(block_tables), _p(sink)
+    a.T, a.B, a.max_blocks, a.H, a.dim, a.R = T, block_tables.shape[0], block_tables.shape[1], H, dim, R
+    a.block_size, a.window, a.max_keys, a.scale = block_size, window, max_keys, scale
+    a.min_q, a.max_query_len, a.max_seq_len = min_q, max_query_len, max_seq_len
+    _lib.lib().atoma_latent_attention_expanded(C.byref(a), _s())
+    _check()
+    return out

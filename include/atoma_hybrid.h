@@ -199,8 +199,32 @@ typedef struct atoma_latent_attn_args {
     float scale;
     uint32_t dtype;
     int32_t max_query_len, max_seq_len;
+    int32_t skip_min_q;           /* > 0: sequences with at least this many query tokens in the step are left alone */
 } atoma_latent_attn_args;
 void atoma_latent_attention_paged(const atoma_latent_attn_args *args, atoma_stream_t stream);
+
+/*
+ * The same attention for LONG prompt portions, on expanded keys and values (bfloat16, dim = vdim of 64 or 128): for every
+ * sequence with at least min_q query tokens in the step, the latents its queries can see (window + portion) are gathered
+ * from the paged cache, k = w_uk c and v = w_uv c are formed by two dense products, and softmax attention with the window
+ * and the sink runs per head on the 5th-generation tensor cores; out[t, h dim ..] is written for those sequences' tokens
+ * only.  A (query, key, head) pair costs 2 (dim + vdim) multiply-adds here instead of 4 kv_rank in the latent space.
+ * max_keys: an upper bound of the gathered rows (sum over the long sequences of min(context, window - 1) + tokens).
+ */
+typedef struct atoma_latent_expanded_args {
+    const void *q;                /* [T, H dim] */
+    const void *latent_cache;
+    const void *w_uk, *w_uv;      /* [H dim, R], [H dim, R] */
+    void *out;                    /* [T, H dim] */
+    const int32_t *query_start;   /* [B + 1] */
+    const int32_t *context_lens;  /* [B] */
+    const int32_t *block_tables;  /* [B, max_blocks] */
+    const float *sink;            /* [H] or NULL */
+    int64_t T, B, max_blocks, H, dim, R, block_size, window, max_keys;
+    float scale;
+    int32_t min_q, max_query_len, max_seq_len;
+} atoma_latent_expanded_args;
+void atoma_latent_attention_expanded(const atoma_latent_expanded_args *args, atoma_stream_t stream);
 
 /* Router of a mixture of experts, float32: z = w_router h (h [T, width] `dtype`, w_router [experts, width] float32),
  * s = sigmoid(z) (score_fn 0) ; the `top` largest scores (ties: the lower index) -> top_expert [T, top] int32 and
@@ -333,9 +357,13 @@ typedef struct atoma_hybrid_batch {
     float *logits;                /* out [num_selected, vocab] */
     uint32_t *next_tokens;        /* out [num_selected] greedy */
     float *residual_trace;        /* optional out [num_layers, T, width]: the residual stream after every layer */
+    /* long prompt portions (pre-norm designs; all zero = none): sequences with at least long_min_q tokens in the step, how many
+     * there are, the sum of their tokens and of their contexts (tokens already cached) */
+    int32_t long_seqs, long_min_q;
+    int64_t long_tokens, long_ctx_sum;
 } atoma_hybrid_batch;
 
-int64_t atoma_hybrid_abi_sizeof(int which); /* 0 layer, 1 model, 2 batch, 3 attention args, 4 gated residual args, 5 latent attention args, 6 expert args */
+int64_t atoma_hybrid_abi_sizeof(int which); /* 0 layer, 1 model, 2 batch, 3 attention args, 4 gated residual args, 5 latent attention args, 6 expert args, 7 expanded attention args */
 int64_t atoma_hybrid_scratch_bytes(const atoma_hybrid_model *model, int64_t num_tokens, int64_t num_selected);
 void atoma_hybrid_step(const atoma_hybrid_model *model, const atoma_hybrid_batch *batch, atoma_stream_t stream);
 

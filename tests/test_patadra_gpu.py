@@ -301,6 +301,36 @@ def test_one_loud_key_is_seen_just_inside_the_window_and_not_just_outside(dtype,
         assert (got.double() - want).abs().max() < (2e-3 if uses_tensor_cores(dtype, R, False) else 1e-5), (i, loud)
 
 
+@pytest.mark.parametrize("H,dim,R,window", [(3, 64, 64, 0), (2, 128, 128, 100), (5, 64, 192, 300), (1, 128, 64, 129)])
+def test_long_portions_on_expanded_keys_and_values(H, dim, R, window):
+    """Sequences with at least 128 tokens in the step: latents gathered from the pages, keys and values expanded, softmax with the
+    window and the sink on the tensor-memory kernel; the other sequences' rows are left alone."""
+    g = torch.Generator().manual_seed(12)
+    seqs = [(0, 300), (37, 1), (200, 150), (16, 2), (500, 128)]
+    cache, bt, pos, tseq, lat = paged_latents(g, seqs, R, 16, torch.bfloat16)
+    T = pos.numel()
+    wk, wv = bf(torch.randn(H * dim, R, generator=g) * 2 / math.sqrt(R)), bf(torch.randn(H * dim, R, generator=g) / math.sqrt(R))
+    q = bf(torch.randn(T, H * dim, generator=g))
+    sk = torch.randn(H, generator=g)
+    qs = torch.tensor([0] + list(np.cumsum([n for _, n in seqs])), dtype=torch.int32)
+    ctx = torch.tensor([c for c, _ in seqs], dtype=torch.int32)
+    long_ = [(c, n) for c, n in seqs if n >= 128]
+    max_keys = sum(n + (min(c, window - 1) if window else c) for c, n in long_)
+    out = torch.full((T, H * dim), 7.0, dtype=torch.bfloat16, device=DEV)
+    _ops().latent_attention_expanded(q.to(torch.bfloat16).to(DEV), cache, wk.to(torch.bfloat16).to(DEV), wv.to(torch.bfloat16).to(DEV), qs.to(DEV),
+                                     ctx.to(DEV), bt, sk.to(DEV), H, dim, R, 16, window, dim ** -0.5, 128, max(n for _, n in seqs),
+                                     max(c + n for c, n in seqs), max_keys, out=out)
+    eye = torch.eye(H * dim, dtype=F64)
+    for b, (c, n) in enumerate(seqs):
+        rows = slice(int(qs[b]), int(qs[b + 1]))
+        if n < 128:
+            assert bool((out[rows] == 7.0).all()), b
+            continue
+        want = po.latent_attention_heads(q[rows].double(), lat[b].double(), eye, wk.double(), wv.double(), sk.double(), H, dim, dim,
+                                         dim ** -0.5, window, first_query=c)
+        assert nerr(out[rows], want) < 1.5e-2, b
+
+
 def test_the_sink_takes_its_share_of_the_weights():
     """One key, score 0, sink s: the key's weight is 1 / (1 + e^s), counted once whatever the number of heads or tiles."""
     R = 8
@@ -383,6 +413,8 @@ VARIANTS = {
     "one_head_equal_dims": dict(heads=1, dim=16, vdim=16, q_rank=16, kv_rank=16, window=5, loop=(0, 2, 3), layers=2),
     "window_of_one": dict(window=1, experts=2, top=2, layers=2, loop=(0, 1, 1)),
     "window_beyond_the_prompt": dict(window=1000, layers=2, loop=(1, 2, 1), no_mlp_layers=(0,)),
+    "heads_of_64": dict(width=64, groups=2, heads=2, dim=64, vdim=64, q_rank=32, kv_rank=64, window=150, layers=2, loop=(0, 1, 2), experts=4, ff=32,
+                        shared_ff=32, max_positions=512),
     "odd_sizes": dict(width=50, vocab=37, heads=5, dim=6, vdim=10, q_rank=14, kv_rank=22, window=33, experts=7, top=3, ff=11,
                       shared_ff=13, groups=5, layers=4, loop=(1, 3, 2), side=3, no_mlp_layers=(2,)),
 }
@@ -417,6 +449,30 @@ def test_decoding_token_by_token_equals_the_whole_prompt(tmp_path, name):
     eng = make_engine(tmp_path, cfg, w, torch.float32, max_tokens=128, block_size=4)
     got = [eng.step_forced([("a", [t], [0])]).logits.clone() for t in toks]
     assert nerr(torch.cat(got), want) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", BOTH)
+def test_long_portions_beside_decoded_tokens(tmp_path, dtype):
+    """Portions of 128 tokens and more (bfloat16: expanded keys and values on the tensor-memory kernel) in one step with short
+    portions and single tokens (latent space), over a window that the long portions cross."""
+    cfg, w, g = build("heads_of_64", 7)
+    toks = {k: torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for k, n in (("a", 400), ("b", 40), ("c", 330))}
+    want = {k: po.forward(cfg, w, t) for k, t in toks.items()}
+    eng = make_engine(tmp_path, cfg, w, dtype, max_tokens=1024)
+    steps = [[("a", 200), ("b", 3)], [("a", 130), ("b", 1), ("c", 129)], [("c", 200), ("a", 69), ("b", 36)], [("a", 1), ("c", 1)]]
+    at, got = {k: 0 for k in toks}, {k: [] for k in toks}
+    for step in steps:
+        entries = []
+        for k, n in step:
+            entries.append((k, toks[k][at[k]:at[k] + n], list(range(n))))
+            at[k] += n
+        out = eng.step_forced(entries)
+        r = 0
+        for k, n in step:
+            got[k].append(out.logits[r:r + n].clone())
+            r += n
+    for k in toks:
+        assert at[k] == len(toks[k]) and model_close(torch.cat(got[k]), want[k], dtype), k
 
 
 def test_long_decoding_far_past_the_window(tmp_path):
