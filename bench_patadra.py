@@ -90,6 +90,13 @@ def _kernel_rows(torch, s, dev, steps, warmup, hbm, tf):
     f = lambda: ho.latent_attention_paged(q, cache, pos, tseq, bt, sink, H, R, page, win, 0.1, S, query_start=qs, max_seq_len=S)
     pairs = sum(min(i + 1, win) for i in range(S))
     rows["latent_attention_prefill"] = _row(_time(torch, f, steps, warmup, flush), flops=4.0 * H * R * pairs, tf=tf)
+    # the same prompt on expanded keys and values (what portions of 128 tokens and more run): gather + two projections + attention
+    wk, wv = torch.randn((H * D, R), device=dev, dtype=bf) * R ** -0.5, torch.randn((H * D, R), device=dev, dtype=bf) * R ** -0.5
+    qe = torch.randn((S, H * D), device=dev, dtype=bf)
+    ctx0 = torch.zeros(1, device=dev, dtype=torch.int32)
+    oe = torch.empty((S, H * D), device=dev, dtype=bf)
+    f = lambda: ho.latent_attention_expanded(qe, cache, wk, wv, qs, ctx0, bt, sink, H, D, R, page, win, 1 / math.sqrt(D), 128, S, S, S, out=oe)
+    rows["latent_attention_expanded_prefill"] = _row(_time(torch, f, steps, warmup, flush), flops=4.0 * H * D * pairs + 4.0 * S * H * D * R, tf=tf)
     G = 8
     q3 = torch.randn((S, H, D), device=dev, dtype=bf)
     k3, v3 = torch.randn((S, G, D), device=dev, dtype=bf), torch.randn((S, G, D), device=dev, dtype=bf)
