@@ -35,7 +35,7 @@ constexpr int kMaxExperts = 1024;
 // ---------------------------------------------------------------------------------------------
 // router: float32 logits, then the `top` largest per token
 // A warp owns TT tokens x ET router rows (the shared expert's gate row rides as row `experts`).  Whatever the tile shape, a
-// (token, row) logit is summed in ONE order — lane l adds k = l, l + 32, ... in ascending order, then the lanes fold in
+// (token, row) logit is summed in ONE order — a lane adds its k values in ascending order, then the lanes fold in
 // an xor tree — so a token's logits are bit-identical in a decode step and in a prompt's portion.
 // ---------------------------------------------------------------------------------------------
 template <typename T, int TT, int ET>
@@ -63,16 +63,53 @@ __global__ void __launch_bounds__(128) moe_logits_kernel(const T *__restrict__ h
     for (int i = 0; i < TT; ++i)
 #pragma unroll
         for (int j = 0; j < ET; ++j) acc[i][j] = 0.f;
-    for (int k = lane; k < width; k += 32) {
-        float hv[TT], wv[ET];
+    // With 16-byte aligned rows a lane takes four consecutive k per step (k = 4 l .. 4 l + 3, then + 128, ...), otherwise one
+    // (k = l, l + 32, ...): which of the two is a property of the model's width, not of the batch.
+    const bool vec = width % 4 == 0 && (reinterpret_cast<uintptr_t>(h) & 15) == 0 && (reinterpret_cast<uintptr_t>(w_router) & 15) == 0 &&
+                     (!w_row_gate || (reinterpret_cast<uintptr_t>(w_row_gate) & 15) == 0);
+    if (vec) {
+        for (int k = 4 * lane; k < width; k += 128) {
+            float hv[TT][4], wv[ET][4];
 #pragma unroll
-        for (int i = 0; i < TT; ++i) hv[i] = hp[i] ? to_f(hp[i][k]) : 0.f;
+            for (int i = 0; i < TT; ++i) {
+                if (hp[i]) {
+                    if constexpr (sizeof(T) == 2) {
+                        const uint2 v = *reinterpret_cast<const uint2 *>(hp[i] + k);
+                        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v.x));
+                        const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&v.y));
+                        hv[i][0] = a.x, hv[i][1] = a.y, hv[i][2] = c.x, hv[i][3] = c.y;
+                    } else {
+                        const float4 v = *reinterpret_cast<const float4 *>(hp[i] + k);
+                        hv[i][0] = v.x, hv[i][1] = v.y, hv[i][2] = v.z, hv[i][3] = v.w;
+                    }
+                } else {
+                    hv[i][0] = hv[i][1] = hv[i][2] = hv[i][3] = 0.f;
+                }
+            }
 #pragma unroll
-        for (int j = 0; j < ET; ++j) wv[j] = wp[j] ? wp[j][k] : 0.f;
+            for (int j = 0; j < ET; ++j) {
+                const float4 v = wp[j] ? *reinterpret_cast<const float4 *>(wp[j] + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+                wv[j][0] = v.x, wv[j][1] = v.y, wv[j][2] = v.z, wv[j][3] = v.w;
+            }
 #pragma unroll
-        for (int i = 0; i < TT; ++i)
+            for (int i = 0; i < TT; ++i)
 #pragma unroll
-            for (int j = 0; j < ET; ++j) acc[i][j] = fmaf(hv[i], wv[j], acc[i][j]);
+                for (int j = 0; j < ET; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[i][j] = fmaf(hv[i][e], wv[j][e], acc[i][j]);
+        }
+    } else {
+        for (int k = lane; k < width; k += 32) {
+            float hv[TT], wv[ET];
+#pragma unroll
+            for (int i = 0; i < TT; ++i) hv[i] = hp[i] ? to_f(hp[i][k]) : 0.f;
+#pragma unroll
+            for (int j = 0; j < ET; ++j) wv[j] = wp[j] ? wp[j][k] : 0.f;
+#pragma unroll
+            for (int i = 0; i < TT; ++i)
+#pragma unroll
+                for (int j = 0; j < ET; ++j) acc[i][j] = fmaf(hv[i], wv[j], acc[i][j]);
+        }
     }
 #pragma unroll
     for (int i = 0; i < TT; ++i)
@@ -312,9 +349,9 @@ bool hyb_moe_route(const void *h, const float *w_router, const float *w_row_gate
     float *z = static_cast<float *>(get_workspace(stream, static_cast<size_t>(T) * rows * 4, kWorkspaceMoeRoute));
     if (!z) return false;
     cudaError_t e;
-    if (T >= 256) {   // prompt portions: 4 x 4 (token, row) pairs per warp share their loads
-        const int64_t warps = ((T + 3) / 4) * ((rows + 3) / 4);
-#define CALL(TT) launch_ex(moe_logits_kernel<TT, 4, 4>, dim3(static_cast<unsigned>((warps + 3) / 4)), dim3(128), 0, stream, \
+    if (T >= 256) {   // prompt portions: 8 x 4 (token, row) pairs per warp share their loads
+        const int64_t warps = ((T + 7) / 8) * ((rows + 3) / 4);
+#define CALL(TT) launch_ex(moe_logits_kernel<TT, 8, 4>, dim3(static_cast<unsigned>((warps + 3) / 4)), dim3(128), 0, stream, \
                            static_cast<const TT *>(h), w_router, w_row_gate, z, static_cast<int>(T), static_cast<int>(width), \
                            static_cast<int>(experts), rows)
         e = HYB_DISPATCH(dtype, CALL);

@@ -360,6 +360,19 @@ def test_router_scores_and_choice(dtype, E, top):
 
 
 @pytest.mark.parametrize("dtype", BOTH)
+@pytest.mark.parametrize("W", [64, 50])
+def test_router_scores_do_not_depend_on_the_batch(dtype, W):
+    """A token's scores are bit-identical whether it is routed in a decode-sized step or inside a prompt's portion (the two
+    sizes run different tile shapes of the logits kernel)."""
+    g = torch.Generator().manual_seed(13)
+    h, wr, wg = bf(torch.randn(300, W, generator=g)), bf(torch.randn(9, W, generator=g) / 4), bf(torch.randn(W, generator=g) / 4)
+    hd = h.to(dtype).to(DEV)
+    i_all, w_all, g_all = _ops().moe_route(hd, wr.to(DEV), wg.to(DEV), 3)
+    i_few, w_few, g_few = _ops().moe_route(hd[5:12].contiguous(), wr.to(DEV), wg.to(DEV), 3)
+    assert torch.equal(i_all[5:12], i_few) and torch.equal(w_all[5:12], w_few) and torch.equal(g_all[5:12], g_few)
+
+
+@pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("T,E,top,W,ff,force_tmem", [(7, 5, 2, 48, 24, False), (150, 3, 1, 40, 70, False), (33, 12, 3, 50, 9, False),
                                                      (1, 4, 4, 64, 64, False), (1, 4, 4, 64, 64, True), (300, 4, 2, 128, 192, True),
                                                      (70, 6, 3, 72, 200, True), (700, 8, 2, 256, 136, False)])
