@@ -88,11 +88,20 @@ def weights_from_checkpoint(spec: HybridSpec, cfg: dict, ckpt: Dict[str, torch.T
             raise AtomaError(f"tensor {name} has shape {tuple(t.shape)}, the configuration needs {tuple(shape)}")
         return t
 
+    def at_least(name, rows, cols):
+        """A table that may hold more rows / columns than the configuration uses."""
+        if name not in ckpt:
+            raise AtomaError(f"tensor {name} is missing from the checkpoint")
+        t = ckpt[name]
+        if t.dim() != 2 or t.shape[0] < rows or t.shape[1] < cols:
+            raise AtomaError(f"tensor {name} has shape {tuple(t.shape)}, the configuration needs at least {(rows, cols)}")
+        return t
+
     n_layers = len(cfg["layers"])
     out = {"embed": get("embed", (spec.vocab, W)), "head": get("head", (spec.vocab, W)), "final_norm": get("final.norm", (W,)),
-           "pos": get("pos", (spec.max_positions, W)), "layers": []}
+           "pos": at_least("pos", spec.max_positions, W)[:, :W], "layers": []}
     if spec.side_dim > 0:
-        out["side_table"] = get("side.embed", (spec.vocab, n_layers * spec.side_dim))
+        out["side_table"] = at_least("side.embed", spec.vocab, n_layers * spec.side_dim)
     by_source = {ls.source: ls for ls in spec.layers}
     for i in range(n_layers):
         ls = by_source.get(i)
